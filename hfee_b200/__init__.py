@@ -7,7 +7,7 @@ B200 (sm_100a), assembled from parts so that other architectures can be added.
 """
 from .config import (ConfigError, EngineConfig, LayerSpec, LlamaConfig, ModelSpec, PartSpec, RunSpec,
                      register_architecture)
-from .cache import CacheManager, FixedState, OutOfPages, PagedKV
+from .cache import CacheBundle, CacheManager, FixedState, OutOfPages, PagedKV
 from .engine import Engine, GenerationResult, ModelRunner, Request, Scheduler, StepEntry
 from .parts import Block, Mixer, Part, Runtime, register_part
 from .sampling import SamplingOptions
@@ -16,6 +16,6 @@ from .weights import TensorNeed, WeightError, write_random_model
 __version__ = "0.1.0"
 
 __all__ = ["ConfigError", "EngineConfig", "LayerSpec", "LlamaConfig", "ModelSpec", "PartSpec", "RunSpec",
-           "register_architecture", "CacheManager", "FixedState", "OutOfPages", "PagedKV", "Engine",
+           "register_architecture", "CacheBundle", "CacheManager", "FixedState", "OutOfPages", "PagedKV", "Engine",
            "GenerationResult", "ModelRunner", "Request", "Scheduler", "StepEntry", "Block", "Mixer", "Part", "Runtime",
            "register_part", "SamplingOptions", "TensorNeed", "WeightError", "write_random_model", "__version__"]

@@ -12,13 +12,13 @@ passed them.
 """
 from __future__ import annotations
 
-from dataclasses import dataclass
+from dataclasses import dataclass, field
 from typing import Any, Dict, List, Mapping, Optional
 
 import numpy as np
 import torch
 
-from .needs import FixedState, PagedKV
+from .needs import CacheBundle, FixedState, PagedKV
 from .pages import OutOfPages, PagePool
 
 _TORCH = {"float32": torch.float32, "bfloat16": torch.bfloat16, "int32": torch.int32}
@@ -29,12 +29,14 @@ class CacheView:
     """What a mixer gets for one cache id: either pages (``k``, ``v`` of shape
     [num_pages, kv_heads, page_size, head_dim], ``block_table`` int32
     [max_requests, max_pages] on the device, ``page_size``) or ``state``
-    ([max_requests, *shape], row = request slot)."""
+    ([max_requests, *shape], row = request slot); a layer that asked with a
+    :class:`CacheBundle` gets its pages, if any, and ``states[name]`` for each named state."""
     k: Optional[torch.Tensor] = None
     v: Optional[torch.Tensor] = None
     block_table: Optional[torch.Tensor] = None
     page_size: int = 0
     state: Optional[torch.Tensor] = None
+    states: Dict[str, torch.Tensor] = field(default_factory=dict)
 
 
 class _PagedGroup:
@@ -60,10 +62,13 @@ class _PagedGroup:
 
     def first_needed_page(self, length: int) -> int:
         """First logical page a token at position >= ``length`` can still read."""
-        if self.need.window is None:
-            return 0
-        lowest_key = max(0, length - int(self.need.window) + 1)
-        return lowest_key // self.page_size
+        lowest = 0
+        if self.need.window is not None:
+            lowest = max(0, length - int(self.need.window) + 1) // self.page_size
+        if self.need.chunk is not None:
+            # the next token sits at position `length` and reads from the start of its block on
+            lowest = max(lowest, (length // int(self.need.chunk)) * int(self.need.chunk) // self.page_size)
+        return lowest
 
 
 class _StateGroup:
@@ -82,27 +87,41 @@ class CacheManager:
         self.device = torch.device(device)
         self.paged: List[_PagedGroup] = []
         self.states: List[_StateGroup] = []
-        by_need: Dict[Any, List[int]] = {}
+        # a group member is (cache id, name of the state within the layer's bundle or None)
+        by_need: Dict[Any, List[Any]] = {}
         for cache_id, need in sorted(needs.items()):
             if need is None:
                 continue
+            if isinstance(need, CacheBundle):
+                if need.paged is not None:
+                    by_need.setdefault(need.paged, []).append((cache_id, None))
+                for name, state in need.states:
+                    if not isinstance(state, FixedState):
+                        raise TypeError(f"cache {cache_id}: state {name!r} of a CacheBundle must be a FixedState")
+                    by_need.setdefault(state, []).append((cache_id, name))
+                continue
             if not isinstance(need, (PagedKV, FixedState)):
-                raise TypeError(f"cache {cache_id}: a mixer's cache_need() must be PagedKV, FixedState or None, "
-                                f"got {type(need).__name__}")
-            by_need.setdefault(need, []).append(cache_id)
-        for need, ids in by_need.items():
-            if isinstance(need, PagedKV):
-                self.paged.append(_PagedGroup(need, ids, num_pages, page_size, max_requests, self.max_pages,
-                                              dtype, self.device))
-            else:
-                self.states.append(_StateGroup(need, ids, max_requests, self.device))
+                raise TypeError(f"cache {cache_id}: a mixer's cache_need() must be PagedKV, FixedState, CacheBundle "
+                                f"or None, got {type(need).__name__}")
+            by_need.setdefault(need, []).append((cache_id, None))
         self._views: Dict[int, CacheView] = {}
-        for g in self.paged:
-            for j, cid in enumerate(g.cache_ids):
-                self._views[cid] = CacheView(k=g.k[j], v=g.v[j], block_table=g.table_dev, page_size=page_size)
-        for s in self.states:
-            for j, cid in enumerate(s.cache_ids):
-                self._views[cid] = CacheView(state=s.state[j])
+        for need, members in by_need.items():
+            ids = [cid for cid, _ in members]
+            if isinstance(need, PagedKV):
+                g = _PagedGroup(need, ids, num_pages, page_size, max_requests, self.max_pages, dtype, self.device)
+                self.paged.append(g)
+                for j, (cid, _) in enumerate(members):
+                    view = self._views.setdefault(cid, CacheView())
+                    view.k, view.v, view.block_table, view.page_size = g.k[j], g.v[j], g.table_dev, page_size
+            else:
+                s = _StateGroup(need, ids, max_requests, self.device)
+                self.states.append(s)
+                for j, (cid, name) in enumerate(members):
+                    view = self._views.setdefault(cid, CacheView())
+                    if name is None:
+                        view.state = s.state[j]
+                    else:
+                        view.states[name] = s.state[j]
         self.length = [0] * max_requests
         self.open_slots = [False] * max_requests
 

@@ -2,16 +2,18 @@
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Optional, Tuple
+from typing import Dict, Optional, Tuple
 
 
 @dataclass(frozen=True)
 class PagedKV:
     """Keys and values for every cached position (or, with ``window``, for the last
-    ``window`` positions only), stored in pages of ``page_size`` tokens."""
+    ``window`` positions only; with ``chunk``, for the positions of the current block of
+    ``chunk`` positions counted from 0 only), stored in pages of ``page_size`` tokens."""
     kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    chunk: Optional[int] = None
 
 
 @dataclass(frozen=True)
@@ -20,3 +22,19 @@ class FixedState:
     when the request is admitted."""
     shape: Tuple[int, ...]
     dtype: str = "float32"
+
+
+@dataclass(frozen=True)
+class CacheBundle:
+    """What a layer with several stateful parts asks for: at most one :class:`PagedKV` and any number of
+    named :class:`FixedState` (a short convolution's history beside a recurrent state, say).  The view
+    the layer gets has the pages as usual and ``states[name]`` per named state."""
+    paged: Optional[PagedKV] = None
+    states: Tuple[Tuple[str, FixedState], ...] = ()
+
+    @classmethod
+    def of(cls, paged: Optional[PagedKV] = None, **states: FixedState) -> "CacheBundle":
+        return cls(paged, tuple(sorted(states.items())))
+
+    def state_map(self) -> Dict[str, FixedState]:
+        return dict(self.states)

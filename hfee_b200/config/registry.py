@@ -1,5 +1,5 @@
-"""One registry from an architecture's name (``architectures[0]`` of config.json)
-to its typed config class and the function that lays it out as parts.
+"""One registry from an architecture's name (``architectures[0]`` of config.json, or its
+key ``architecture``) to its typed config class and the function that lays it out as parts.
 
 The reference keeps a map from the GGUF architecture string to a model variant
 and refuses unknown names with ``unsupported model architecture``
@@ -68,9 +68,13 @@ def resolve(config_json: Mapping[str, Any], tensor_shapes: Optional[Mapping[str,
     (checkpoint tensor name -> shape), when the caller has a checkpoint at hand, lets an
     architecture take a size that config.json leaves out from the tensors themselves."""
     archs = config_json.get("architectures")
-    if not archs or not isinstance(archs, (list, tuple)):
-        raise ConfigError("config.json: missing key 'architectures'")
-    arch = architecture(str(archs[0]))
+    if isinstance(archs, (list, tuple)) and archs:
+        name = archs[0]
+    elif isinstance(config_json.get("architecture"), str):
+        name = config_json["architecture"]
+    else:
+        raise ConfigError("config.json: missing key 'architectures' (a list) or 'architecture' (a name)")
+    arch = architecture(str(name))
     if tensor_shapes is not None and arch.fill_from_tensors is not None:
         config_json = arch.fill_from_tensors(config_json, tensor_shapes)
     return arch, arch.config_from_dict(config_json)

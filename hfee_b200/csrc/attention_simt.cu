@@ -6,6 +6,12 @@
 // softmax, so the result at a position depends neither on how the tokens were cut
 // into steps nor on which pages hold them.  This kernel is the attention of the
 // true 32-bit path and the fallback of the bfloat16 path.
+//
+// Options beside the plain softmax over a causal window: `chunk` > 0 hides every key whose
+// position lies in another block of `chunk` positions than the query's (blocks counted from
+// position 0 of the request); SIGMOID replaces the softmax by unnormalised weights
+// sigmoid(score * head_scale[h] + head_bias[h]) (either array may be missing); `gate` multiplies
+// the output element by element with sigmoid(gate[token, head * hd + d]).
 // Reference: hostfog/hfee internal/llm/forward.go:146-178 (scores scaled after the
 // dot, softmax over 0..pos, weighted sum of values), internal/ggml/ops.go:136-150.
 #include "common.cuh"
@@ -15,12 +21,13 @@ namespace {
 constexpr int WARPS = 4;
 constexpr int MAX_HD = 256;
 
-template <typename T>
+template <typename T, bool SIGMOID>
 __global__ void __launch_bounds__(WARPS * 32)
 attention_simt_kernel(const T* __restrict__ q, int ld_q, const T* __restrict__ k_pool,
                       const T* __restrict__ v_pool, PagedCache cache, const int* __restrict__ positions,
                       const int* __restrict__ slot_of_token, T* __restrict__ out, int ld_o, int n, int heads,
-                      float scale, int window) {
+                      float scale, int window, int chunk, const float* __restrict__ head_scale,
+                      const float* __restrict__ head_bias, const T* __restrict__ gate, long long ld_gate) {
   pdl_wait();
   pdl_launch_dependents();
   __shared__ float q_s[WARPS][MAX_HD];
@@ -32,6 +39,9 @@ attention_simt_kernel(const T* __restrict__ q, int ld_q, const T* __restrict__ k
   int kvh = h / (heads / cache.kv_heads);
   int pos = positions[i], slot = slot_of_token[i];
   int lo = (window > 0 && pos + 1 > window) ? pos + 1 - window : 0;
+  if (chunk > 0) lo = max(lo, (pos / chunk) * chunk);
+  const float h_scale = (SIGMOID && head_scale != nullptr) ? head_scale[h] : 1.f;
+  const float h_bias = (SIGMOID && head_bias != nullptr) ? head_bias[h] : 0.f;
 
   const T* qrow = q + (long long)i * ld_q + (long long)h * hd;
   for (int d = lane; d < hd; d += 32) q_s[warp][d] = to_f32<T>(qrow[d]);
@@ -52,12 +62,18 @@ attention_simt_kernel(const T* __restrict__ q, int ld_q, const T* __restrict__ k
       for (int d = 0; d < hd; ++d) acc = fmaf(q_s[warp][d], to_f32<T>(kr[d]), acc);
       s = acc * scale;
     }
-    float m_new = fmaxf(m, warp_max(s));
-    float p = key <= pos ? expf(s - m_new) : 0.f;
-    float alpha = expf(m - m_new);          // exp(-inf) = 0 on the first block
-    l = l * alpha + warp_sum(p);
+    float p;
+    if constexpr (SIGMOID) {
+      p = key <= pos ? 1.f / (1.f + expf(-(s * h_scale + h_bias))) : 0.f;
+    } else {
+      float m_new = fmaxf(m, warp_max(s));
+      p = key <= pos ? expf(s - m_new) : 0.f;
+      float alpha = expf(m - m_new);          // exp(-inf) = 0 on the first block
+      l = l * alpha + warp_sum(p);
 #pragma unroll
-    for (int j = 0; j < DPL; ++j) o[j] *= alpha;
+      for (int j = 0; j < DPL; ++j) o[j] *= alpha;
+      m = m_new;
+    }
     int count = min(32, pos + 1 - base);
     for (int t = 0; t < count; ++t) {
       float pt = __shfl_sync(0xffffffffu, p, t);
@@ -68,41 +84,75 @@ attention_simt_kernel(const T* __restrict__ q, int ld_q, const T* __restrict__ k
         if (d < hd) o[j] = fmaf(pt, to_f32<T>(vr[d]), o[j]);
       }
     }
-    m = m_new;
   }
   T* orow = out + (long long)i * ld_o + (long long)h * hd;
-  float inv = 1.f / l;
+  float inv = SIGMOID ? 1.f : 1.f / l;
+  const T* grow = gate != nullptr ? gate + (long long)i * ld_gate + (long long)h * hd : nullptr;
 #pragma unroll
   for (int j = 0; j < DPL; ++j) {
     int d = lane + 32 * j;
-    if (d < hd) orow[d] = from_f32<T>(o[j] * inv);
+    if (d < hd) {
+      float v = o[j] * inv;
+      if (grow != nullptr) v *= 1.f / (1.f + expf(-to_f32<T>(grow[d])));
+      orow[d] = from_f32<T>(v);
+    }
   }
 }
 
 }  // namespace
 
-HFEE_API int hfee_attention_simt(const void* q, int ld_q, const void* k_pool, const void* v_pool,
-                                 const int* block_table, int max_pages, int page_size, const int* positions,
-                                 const int* slot_of_token, void* out, int ld_o, int n, int heads, int kv_heads,
-                                 int head_dim, float scale, int window, int dtype, cudaStream_t stream) {
+namespace {
+template <typename T>
+void launch_simt(const void* q, int ld_q, const void* k_pool, const void* v_pool, const PagedCache& c, const int* positions,
+                 const int* slot_of_token, void* out, int ld_o, int n, int heads, float scale, int window, int chunk,
+                 int sigmoid, const float* head_scale, const float* head_bias, const void* gate, long long ld_gate,
+                 cudaStream_t stream) {
+  long long tasks = (long long)n * heads;
+  unsigned blocks = (unsigned)((tasks + WARPS - 1) / WARPS);
+  if (sigmoid)
+    hfee_launch(attention_simt_kernel<T, true>, dim3(blocks), dim3(WARPS * 32), 0, stream, (const T*)q, ld_q, (const T*)k_pool,
+                (const T*)v_pool, c, positions, slot_of_token, (T*)out, ld_o, n, heads, scale, window, chunk, head_scale,
+                head_bias, (const T*)gate, ld_gate);
+  else
+    hfee_launch(attention_simt_kernel<T, false>, dim3(blocks), dim3(WARPS * 32), 0, stream, (const T*)q, ld_q, (const T*)k_pool,
+                (const T*)v_pool, c, positions, slot_of_token, (T*)out, ld_o, n, heads, scale, window, chunk, head_scale,
+                head_bias, (const T*)gate, ld_gate);
+}
+}  // namespace
+
+// weights: 0 = softmax over the visible keys, 1 = sigmoid(score * head_scale[h] + head_bias[h]) per key.
+HFEE_API int hfee_attention_simt_masked(const void* q, int ld_q, const void* k_pool, const void* v_pool,
+                                        const int* block_table, int max_pages, int page_size, const int* positions,
+                                        const int* slot_of_token, void* out, int ld_o, int n, int heads, int kv_heads,
+                                        int head_dim, float scale, int window, int chunk, int weights,
+                                        const float* head_scale, const float* head_bias, const void* gate,
+                                        long long ld_gate, int dtype, cudaStream_t stream) {
   if (n == 0) return HFEE_OK;
   HFEE_REQUIRE(head_dim > 0 && head_dim <= MAX_HD, "attention_simt: head_dim %d is outside 1..%d", head_dim, MAX_HD);
   HFEE_REQUIRE(heads > 0 && kv_heads > 0 && heads % kv_heads == 0,
                "attention_simt: heads %d must be a multiple of kv_heads %d", heads, kv_heads);
   HFEE_REQUIRE(page_size > 0 && max_pages > 0, "attention_simt: bad cache sizes");
+  HFEE_REQUIRE(window >= 0 && chunk >= 0 && (weights == 0 || weights == 1), "attention_simt: bad mask or weight option");
+  HFEE_REQUIRE(gate == nullptr || ld_gate >= (long long)heads * head_dim, "attention_simt: ld_gate is too small");
   PagedCache c;
   HFEE_REQUIRE(make_paged_cache(&c, block_table, max_pages, page_size, kv_heads, head_dim),
                "page_size %d must be a power of two", page_size);
-  long long tasks = (long long)n * heads;
-  unsigned blocks = (unsigned)((tasks + WARPS - 1) / WARPS);
   if (dtype == HFEE_F32)
-    hfee_launch(attention_simt_kernel<float>, dim3(blocks), dim3(WARPS * 32), 0, stream, (const float*)q, ld_q, (const float*)k_pool,
-        (const float*)v_pool, c, positions, slot_of_token, (float*)out, ld_o, n, heads, scale, window);
+    launch_simt<float>(q, ld_q, k_pool, v_pool, c, positions, slot_of_token, out, ld_o, n, heads, scale, window, chunk,
+                       weights, head_scale, head_bias, gate, ld_gate, stream);
   else if (dtype == HFEE_BF16)
-    hfee_launch(attention_simt_kernel<__nv_bfloat16>, dim3(blocks), dim3(WARPS * 32), 0, stream, (const __nv_bfloat16*)q, ld_q,
-        (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, c, positions, slot_of_token,
-        (__nv_bfloat16*)out, ld_o, n, heads, scale, window);
+    launch_simt<__nv_bfloat16>(q, ld_q, k_pool, v_pool, c, positions, slot_of_token, out, ld_o, n, heads, scale, window,
+                               chunk, weights, head_scale, head_bias, gate, ld_gate, stream);
   else
     return hfee_fail(HFEE_ERR_ARG, "attention_simt: unknown dtype %d", dtype);
   return hfee_check_launch("attention_simt");
+}
+
+HFEE_API int hfee_attention_simt(const void* q, int ld_q, const void* k_pool, const void* v_pool,
+                                 const int* block_table, int max_pages, int page_size, const int* positions,
+                                 const int* slot_of_token, void* out, int ld_o, int n, int heads, int kv_heads,
+                                 int head_dim, float scale, int window, int dtype, cudaStream_t stream) {
+  return hfee_attention_simt_masked(q, ld_q, k_pool, v_pool, block_table, max_pages, page_size, positions, slot_of_token,
+                                    out, ld_o, n, heads, kv_heads, head_dim, scale, window, 0, 0, nullptr, nullptr,
+                                    nullptr, 0, dtype, stream);
 }

@@ -4,7 +4,7 @@
 #include "common.cuh"
 
 // ---------------------------------------------------------------- embedding
-// out[i,:] = table[token_i,:] as float32 (the residual stream is float32).
+// out[i,:] = table[token_i,:] * scale as float32 (the residual stream is float32; scale is 1 for most models).
 // Reference: x[i,:] = embed.Row(tokens[i]), hostfog/hfee internal/llm/forward.go:75-77.
 // A negative token id means "the token last sampled on the device for this token's request":
 // it is read from feedback[slot_of_token[i]], so a decode step can be launched before the host
@@ -12,7 +12,7 @@
 template <typename T>
 __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ tokens,
                              const int* __restrict__ slot_of_token, const int* __restrict__ feedback,
-                             float* __restrict__ out, int width, int vocab) {
+                             float* __restrict__ out, int width, int vocab, float scale) {
   pdl_wait();
   pdl_launch_dependents();
   int i = blockIdx.x;
@@ -21,7 +21,7 @@ __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict_
   bool ok = tok >= 0 && tok < vocab;
   const T* row = table + (long long)(ok ? tok : 0) * width;
   for (int c = threadIdx.x; c < width; c += blockDim.x)
-    out[(long long)i * width + c] = ok ? to_f32<T>(row[c]) : 0.f;
+    out[(long long)i * width + c] = ok ? to_f32<T>(row[c]) * scale : 0.f;
 }
 
 // The same with 16-byte reads: one piece of the row per thread and trip, all of a thread's pieces
@@ -29,7 +29,7 @@ __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict_
 template <typename T, int VEC>
 __global__ void embed_vec_kernel(const T* __restrict__ table, const int* __restrict__ tokens,
                                  const int* __restrict__ slot_of_token, const int* __restrict__ feedback,
-                                 float* __restrict__ out, int width, int vocab) {
+                                 float* __restrict__ out, int width, int vocab, float scale) {
   struct alignas(16) Piece { T v[VEC]; };
   pdl_wait();
   pdl_launch_dependents();
@@ -53,7 +53,7 @@ __global__ void embed_vec_kernel(const T* __restrict__ table, const int* __restr
       if (p >= pieces) continue;
 #pragma unroll
       for (int e = 0; e < VEC; e += 4) {
-        float4 o = ok ? make_float4(to_f32<T>(v[j].v[e]), to_f32<T>(v[j].v[e + 1]), to_f32<T>(v[j].v[e + 2]), to_f32<T>(v[j].v[e + 3]))
+        float4 o = ok ? make_float4(to_f32<T>(v[j].v[e]) * scale, to_f32<T>(v[j].v[e + 1]) * scale, to_f32<T>(v[j].v[e + 2]) * scale, to_f32<T>(v[j].v[e + 3]) * scale)
                       : make_float4(0.f, 0.f, 0.f, 0.f);
         *reinterpret_cast<float4*>(dst + p * VEC + e) = o;
       }
@@ -62,18 +62,18 @@ __global__ void embed_vec_kernel(const T* __restrict__ table, const int* __restr
 }
 
 HFEE_API int hfee_embed(const void* table, int dtype, const int* tokens, const int* slot_of_token,
-                        const int* feedback, float* out, int n, int width, int vocab, cudaStream_t stream) {
+                        const int* feedback, float* out, int n, int width, int vocab, float scale, cudaStream_t stream) {
   if (n == 0) return HFEE_OK;
   HFEE_REQUIRE(n > 0 && width > 0 && vocab > 0, "embed: bad sizes n=%d width=%d vocab=%d", n, width, vocab);
   int threads = width >= 256 ? 256 : 64;
   const int vec = dtype == HFEE_F32 ? 4 : 8;
   const bool vector = width % vec == 0 && (uintptr_t)table % 16 == 0 && (uintptr_t)out % 16 == 0;
   if (dtype == HFEE_F32) {
-    if (vector) hfee_launch(embed_vec_kernel<float, 4>, dim3(n), dim3(threads), 0, stream, (const float*)table, tokens, slot_of_token, feedback, out, width, vocab);
-    else hfee_launch(embed_kernel<float>, dim3(n), dim3(threads), 0, stream, (const float*)table, tokens, slot_of_token, feedback, out, width, vocab);
+    if (vector) hfee_launch(embed_vec_kernel<float, 4>, dim3(n), dim3(threads), 0, stream, (const float*)table, tokens, slot_of_token, feedback, out, width, vocab, scale);
+    else hfee_launch(embed_kernel<float>, dim3(n), dim3(threads), 0, stream, (const float*)table, tokens, slot_of_token, feedback, out, width, vocab, scale);
   } else if (dtype == HFEE_BF16) {
-    if (vector) hfee_launch(embed_vec_kernel<__nv_bfloat16, 8>, dim3(n), dim3(threads), 0, stream, (const __nv_bfloat16*)table, tokens, slot_of_token, feedback, out, width, vocab);
-    else hfee_launch(embed_kernel<__nv_bfloat16>, dim3(n), dim3(threads), 0, stream, (const __nv_bfloat16*)table, tokens, slot_of_token, feedback, out, width, vocab);
+    if (vector) hfee_launch(embed_vec_kernel<__nv_bfloat16, 8>, dim3(n), dim3(threads), 0, stream, (const __nv_bfloat16*)table, tokens, slot_of_token, feedback, out, width, vocab, scale);
+    else hfee_launch(embed_kernel<__nv_bfloat16>, dim3(n), dim3(threads), 0, stream, (const __nv_bfloat16*)table, tokens, slot_of_token, feedback, out, width, vocab, scale);
   } else {
     return hfee_fail(HFEE_ERR_ARG, "embed: unknown dtype %d", dtype);
   }

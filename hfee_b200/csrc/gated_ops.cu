@@ -1,0 +1,246 @@
+// Row-wise pieces of layers that gate or norm a sublayer's output, all in float32 arithmetic:
+//
+//   hfee_rmsnorm_add      residual += y / sqrt(mean(y^2) + eps) * w          (a norm on a sublayer's output)
+//   hfee_norm_gate        out = [x / sqrt(mean(x^2) + eps) * w] * sigmoid(g)  (the norm is optional)
+//   hfee_gated_act        out = act(gate) * up, act = SiLU or tanh-GELU
+//   hfee_scale_f32        x *= alpha
+//   hfee_cast_rows        out = x rounded to the activations' type (what a matrix product reads of the residual stream)
+//   hfee_qk_norm_rope_cache   RMS norm over a token's whole query (and key) projection, rotary on the
+//                         leading dimensions of every head, keys into their cache page, and the
+//                         values' page filled with the keys as projected (v_offset < 0) or with the
+//                         columns of the row that start at v_offset
+#include "common.cuh"
+
+namespace {
+
+constexpr int ROW_THREADS = 256;
+
+__device__ __forceinline__ float block_sum(float v, float* partial) {
+  v = warp_sum(v);
+  __syncthreads();                                   // partial may still be read from a call before
+  if ((threadIdx.x & 31) == 0) partial[threadIdx.x >> 5] = v;
+  __syncthreads();
+  float total = 0.f;
+#pragma unroll
+  for (int i = 0; i < ROW_THREADS / 32; ++i) total += partial[i];
+  return total;
+}
+
+__device__ __forceinline__ float sigmoid_f32(float z) { return 1.f / (1.f + expf(-z)); }
+
+__global__ void __launch_bounds__(ROW_THREADS)
+rmsnorm_add_kernel(const float* __restrict__ y, long long ld_y, const float* __restrict__ w,
+                   float* __restrict__ residual, int width, float eps, int add_unit) {
+  __shared__ float partial[ROW_THREADS / 32];
+  pdl_wait();
+  pdl_launch_dependents();
+  const float* yr = y + (long long)blockIdx.x * ld_y;
+  float* rr = residual + (long long)blockIdx.x * width;
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < width; c += ROW_THREADS) ss = fmaf(yr[c], yr[c], ss);
+  const float scale = 1.0f / sqrtf(block_sum(ss, partial) / (float)width + eps);
+  for (int c = threadIdx.x; c < width; c += ROW_THREADS)
+    rr[c] += yr[c] * scale * (add_unit ? 1.f + w[c] : w[c]);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(ROW_THREADS)
+norm_gate_kernel(const float* __restrict__ x, long long ld_x, const float* __restrict__ w, float eps,
+                 const T* __restrict__ gate, long long ld_g, T* __restrict__ out, long long ld_o, int width) {
+  __shared__ float partial[ROW_THREADS / 32];
+  pdl_wait();
+  pdl_launch_dependents();
+  const float* xr = x + (long long)blockIdx.x * ld_x;
+  const T* gr = gate + (long long)blockIdx.x * ld_g;
+  T* orow = out + (long long)blockIdx.x * ld_o;
+  float scale = 1.f;
+  if (w != nullptr) {
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < width; c += ROW_THREADS) ss = fmaf(xr[c], xr[c], ss);
+    scale = 1.0f / sqrtf(block_sum(ss, partial) / (float)width + eps);
+  }
+  for (int c = threadIdx.x; c < width; c += ROW_THREADS) {
+    const float v = w != nullptr ? xr[c] * scale * w[c] : xr[c];
+    orow[c] = from_f32<T>(v * sigmoid_f32(to_f32<T>(gr[c])));
+  }
+}
+
+enum GateActivation { GA_SILU = 0, GA_GELU_TANH = 1 };
+
+__device__ __forceinline__ float gate_activation(float z, int act) {
+  if (act == GA_GELU_TANH) return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+  return z / (1.f + expf(-z));
+}
+
+template <typename T>
+__global__ void gated_act_kernel(const T* __restrict__ gu, long long ld_gu, T* __restrict__ h, long long ld_h, int n,
+                                 int inter, int granule, int act) {
+  pdl_wait();
+  pdl_launch_dependents();
+  long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (long long)n * inter) return;
+  int i = (int)(idx / inter), c = (int)(idx % inter);
+  long long gcol = (long long)(c / granule) * 2 * granule + c % granule;
+  float g = to_f32<T>(gu[(long long)i * ld_gu + gcol]);
+  float u = to_f32<T>(gu[(long long)i * ld_gu + gcol + granule]);
+  h[(long long)i * ld_h + c] = from_f32<T>(gate_activation(g, act) * u);
+}
+
+__global__ void scale_kernel(float* __restrict__ x, long long ld, int cols, long long total, float alpha) {
+  pdl_wait();
+  pdl_launch_dependents();
+  long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  x[(idx / cols) * ld + idx % cols] *= alpha;
+}
+
+template <typename T>
+__global__ void cast_rows_kernel(const float* __restrict__ x, T* __restrict__ out, long long ld_o, int cols, long long total) {
+  pdl_wait();
+  pdl_launch_dependents();
+  long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  out[(idx / cols) * ld_o + idx % cols] = from_f32<T>(x[idx]);
+}
+
+// One block per token.  qk row: [heads * hd query values | kv_heads * hd key values].
+template <typename T>
+__global__ void __launch_bounds__(ROW_THREADS)
+qk_norm_rope_cache_kernel(const T* __restrict__ qk, long long ld_qk, const float* __restrict__ wq,
+                          const float* __restrict__ wk, float eps, const float2* __restrict__ cs, int rope_dim,
+                          const int* __restrict__ positions, const int* __restrict__ slot_of_token,
+                          T* __restrict__ q_out, long long ld_q, T* __restrict__ k_pool, T* __restrict__ v_pool,
+                          PagedCache cache, int heads, int v_offset) {
+  __shared__ float partial[ROW_THREADS / 32];
+  const int i = blockIdx.x;
+  const int pos = positions[i], slot = slot_of_token[i];
+  pdl_wait();
+  pdl_launch_dependents();
+  const int hd = cache.head_dim, half = rope_dim / 2;
+  const int q_cols = heads * hd, k_cols = cache.kv_heads * hd;
+  const T* row = qk + (long long)i * ld_qk;
+  const float2* csr = cs != nullptr ? cs + (long long)i * half : nullptr;
+
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < q_cols; c += ROW_THREADS) { const float v = to_f32<T>(row[c]); ss = fmaf(v, v, ss); }
+  const float q_scale = wq != nullptr ? 1.0f / sqrtf(block_sum(ss, partial) / (float)q_cols + eps) : 1.f;
+  for (int c = threadIdx.x; c < q_cols; c += ROW_THREADS) {
+    const int d = c % hd;
+    float val = to_f32<T>(row[c]) * q_scale * (wq != nullptr ? wq[c] : 1.f);
+    if (csr != nullptr && d < rope_dim) {
+      const int p = d < half ? c + half : c - half;                 // the dimension this one is paired with
+      const float other = to_f32<T>(row[p]) * q_scale * (wq != nullptr ? wq[p] : 1.f);
+      const float2 t = csr[d < half ? d : d - half];                // (cos, sin) of the pair's angle
+      val = d < half ? val * t.x - other * t.y : val * t.x + other * t.y;
+    }
+    q_out[(long long)i * ld_q + c] = from_f32<T>(val);
+  }
+  if (k_pool == nullptr) return;
+  const T* krow = row + q_cols;
+  ss = 0.f;
+  for (int c = threadIdx.x; c < k_cols; c += ROW_THREADS) { const float v = to_f32<T>(krow[c]); ss = fmaf(v, v, ss); }
+  const float k_scale = wk != nullptr ? 1.0f / sqrtf(block_sum(ss, partial) / (float)k_cols + eps) : 1.f;
+  for (int c = threadIdx.x; c < k_cols; c += ROW_THREADS) {
+    const int g = c / hd, d = c % hd;
+    const T raw = krow[c];
+    float val = to_f32<T>(raw) * k_scale * (wk != nullptr ? wk[c] : 1.f);
+    if (csr != nullptr && d < rope_dim) {
+      const int p = d < half ? c + half : c - half;
+      const float other = to_f32<T>(krow[p]) * k_scale * (wk != nullptr ? wk[p] : 1.f);
+      const float2 t = csr[d < half ? d : d - half];
+      val = d < half ? val * t.x - other * t.y : val * t.x + other * t.y;
+    }
+    const long long at = paged_offset(cache, slot, pos, g) + d;
+    k_pool[at] = from_f32<T>(val);
+    if (v_pool != nullptr) v_pool[at] = v_offset >= 0 ? row[v_offset + c] : raw;
+  }
+}
+
+}  // namespace
+
+HFEE_API int hfee_rmsnorm_add(const float* y, long long ld_y, const float* w, float* residual, int n, int width,
+                              float eps, int add_unit, cudaStream_t stream) {
+  if (n == 0) return HFEE_OK;
+  HFEE_REQUIRE(n > 0 && width > 0 && ld_y >= width, "rmsnorm_add: bad sizes");
+  hfee_launch(rmsnorm_add_kernel, dim3(n), dim3(ROW_THREADS), 0, stream, y, ld_y, w, residual, width, eps, add_unit);
+  return hfee_check_launch("rmsnorm_add");
+}
+
+HFEE_API int hfee_norm_gate(const float* x, long long ld_x, const float* w, float eps, const void* gate, long long ld_g,
+                            void* out, long long ld_o, int n, int width, int dtype, cudaStream_t stream) {
+  if (n == 0) return HFEE_OK;
+  HFEE_REQUIRE(n > 0 && width > 0 && ld_x >= width && ld_g >= width && ld_o >= width, "norm_gate: bad sizes");
+  if (dtype == HFEE_F32)
+    hfee_launch(norm_gate_kernel<float>, dim3(n), dim3(ROW_THREADS), 0, stream, x, ld_x, w, eps, (const float*)gate, ld_g, (float*)out, ld_o, width);
+  else if (dtype == HFEE_BF16)
+    hfee_launch(norm_gate_kernel<__nv_bfloat16>, dim3(n), dim3(ROW_THREADS), 0, stream, x, ld_x, w, eps, (const __nv_bfloat16*)gate, ld_g, (__nv_bfloat16*)out, ld_o, width);
+  else
+    return hfee_fail(HFEE_ERR_ARG, "norm_gate: unknown dtype %d", dtype);
+  return hfee_check_launch("norm_gate");
+}
+
+HFEE_API int hfee_gated_act(const void* gu, long long ld_gu, void* h, long long ld_h, int n, int inter, int granule,
+                            int act, int dtype, cudaStream_t stream) {
+  if (n == 0) return HFEE_OK;
+  HFEE_REQUIRE(n > 0 && inter > 0 && ld_gu >= 2 * inter && ld_h >= inter, "gated_act: bad sizes");
+  HFEE_REQUIRE(granule > 0 && inter % granule == 0, "gated_act: granule %d does not divide %d", granule, inter);
+  HFEE_REQUIRE(act == GA_SILU || act == GA_GELU_TANH, "gated_act: unknown activation %d", act);
+  long long total = (long long)n * inter;
+  unsigned blocks = (unsigned)((total + 255) / 256);
+  if (dtype == HFEE_F32)
+    hfee_launch(gated_act_kernel<float>, dim3(blocks), dim3(256), 0, stream, (const float*)gu, ld_gu, (float*)h, ld_h, n, inter, granule, act);
+  else if (dtype == HFEE_BF16)
+    hfee_launch(gated_act_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, (const __nv_bfloat16*)gu, ld_gu, (__nv_bfloat16*)h, ld_h, n, inter, granule, act);
+  else
+    return hfee_fail(HFEE_ERR_ARG, "gated_act: unknown dtype %d", dtype);
+  return hfee_check_launch("gated_act");
+}
+
+HFEE_API int hfee_scale_f32(float* x, long long ld, int rows, int cols, float alpha, cudaStream_t stream) {
+  if (rows == 0 || cols == 0) return HFEE_OK;
+  HFEE_REQUIRE(rows > 0 && cols > 0 && ld >= cols, "scale: bad sizes");
+  long long total = (long long)rows * cols;
+  hfee_launch(scale_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, x, ld, cols, total, alpha);
+  return hfee_check_launch("scale");
+}
+
+HFEE_API int hfee_cast_rows(const float* x, void* out, long long ld_o, int rows, int cols, int dtype, cudaStream_t stream) {
+  if (rows == 0 || cols == 0) return HFEE_OK;
+  HFEE_REQUIRE(rows > 0 && cols > 0 && ld_o >= cols, "cast_rows: bad sizes");
+  long long total = (long long)rows * cols;
+  unsigned blocks = (unsigned)((total + 255) / 256);
+  if (dtype == HFEE_F32)
+    hfee_launch(cast_rows_kernel<float>, dim3(blocks), dim3(256), 0, stream, x, (float*)out, ld_o, cols, total);
+  else if (dtype == HFEE_BF16)
+    hfee_launch(cast_rows_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, x, (__nv_bfloat16*)out, ld_o, cols, total);
+  else
+    return hfee_fail(HFEE_ERR_ARG, "cast_rows: unknown dtype %d", dtype);
+  return hfee_check_launch("cast_rows");
+}
+
+HFEE_API int hfee_qk_norm_rope_cache(const void* qk, long long ld_qk, const float* wq, const float* wk, float eps,
+                                     const float* cs, int rope_dim, const int* positions, const int* slot_of_token,
+                                     void* q_out, long long ld_q, void* k_pool, void* v_pool, const int* block_table,
+                                     int max_pages, int page_size, int n, int heads, int kv_heads, int head_dim,
+                                     int v_offset, int dtype, cudaStream_t stream) {
+  if (n == 0) return HFEE_OK;
+  HFEE_REQUIRE(n > 0 && heads > 0 && kv_heads > 0 && head_dim > 0, "qk_norm_rope_cache: bad sizes");
+  HFEE_REQUIRE(rope_dim >= 0 && rope_dim % 2 == 0 && rope_dim <= head_dim,
+               "qk_norm_rope_cache: rope_dim %d must be even and at most head_dim %d", rope_dim, head_dim);
+  HFEE_REQUIRE(ld_q >= (long long)heads * head_dim && ld_qk >= (long long)heads * head_dim + (k_pool ? (long long)kv_heads * head_dim : 0),
+               "qk_norm_rope_cache: a leading dimension is too small");
+  PagedCache c;
+  HFEE_REQUIRE(make_paged_cache(&c, block_table, max_pages, page_size, kv_heads, head_dim),
+               "page_size %d must be a power of two", page_size);
+  const float2* cs2 = (const float2*)cs;
+  if (dtype == HFEE_F32)
+    hfee_launch(qk_norm_rope_cache_kernel<float>, dim3(n), dim3(ROW_THREADS), 0, stream, (const float*)qk, ld_qk, wq, wk, eps, cs2,
+                rope_dim, positions, slot_of_token, (float*)q_out, ld_q, (float*)k_pool, (float*)v_pool, c, heads, v_offset);
+  else if (dtype == HFEE_BF16)
+    hfee_launch(qk_norm_rope_cache_kernel<__nv_bfloat16>, dim3(n), dim3(ROW_THREADS), 0, stream, (const __nv_bfloat16*)qk, ld_qk, wq, wk,
+                eps, cs2, rope_dim, positions, slot_of_token, (__nv_bfloat16*)q_out, ld_q, (__nv_bfloat16*)k_pool,
+                (__nv_bfloat16*)v_pool, c, heads, v_offset);
+  else
+    return hfee_fail(HFEE_ERR_ARG, "qk_norm_rope_cache: unknown dtype %d", dtype);
+  return hfee_check_launch("qk_norm_rope_cache");
+}

@@ -26,7 +26,7 @@ _L = ctypes.c_longlong
 _F = ctypes.c_float
 
 _SIGNATURES = {
-    "hfee_embed": [_P, _I, _P, _P, _P, _P, _I, _I, _I, _P],
+    "hfee_embed": [_P, _I, _P, _P, _P, _P, _I, _I, _I, _F, _P],
     "hfee_rmsnorm": [_P, _P, _P, _P, _I, _I, _I, _F, _I, _P],
     "hfee_rope_table": [_P, _P, _P, _I, _I, _P],
     "hfee_rope_cache_write": [_P, _I, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P],
@@ -48,6 +48,17 @@ _SIGNATURES = {
     "hfee_attention_mma_rope": [_P, _I, _P, _I, _I, _I, _P, _P, _P, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _I, _P, _P],
     "hfee_gemm_simt": [_P, _L, _P, _L, _I, _P, _L, _I, _I, _I, _I, _I, _P],
     "hfee_attention_simt": [_P, _I, _P, _P, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _P],
+    "hfee_attention_simt_masked": [_P, _I, _P, _P, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _P, _P, _P, _L, _I, _P],
+    "hfee_short_conv": [_P, _P, _P, _P, _P, _P, _L, _I, _I, _I, _I, _I, _I, _P],
+    "hfee_short_conv_launches": [_I, _I, _I],
+    "hfee_linear_attention": [_P, _P, _P, _L, _I, _P, _P, _P, _P, _P, _L, _I, _I, _I, _I, _I, _I, _P],
+    "hfee_linear_attention_chunked": [_P, _P, _P, _L, _I, _P, _P, _P, _P, _P, _L, _P, _L, _I, _I, _I, _I, _I, _I, _I, _P],
+    "hfee_rmsnorm_add": [_P, _L, _P, _P, _I, _I, _F, _I, _P],
+    "hfee_norm_gate": [_P, _L, _P, _F, _P, _L, _P, _L, _I, _I, _I, _P],
+    "hfee_gated_act": [_P, _L, _P, _L, _I, _I, _I, _I, _I, _P],
+    "hfee_scale_f32": [_P, _L, _I, _I, _F, _P],
+    "hfee_cast_rows": [_P, _P, _L, _I, _I, _I, _P],
+    "hfee_qk_norm_rope_cache": [_P, _L, _P, _P, _F, _P, _I, _P, _P, _P, _L, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P],
     "hfee_sample": [_P, _L, _I, _I, _P, _P, _P, _L, _P, _P, _P, _P],
     "hfee_argmax": [_P, _L, _I, _I, _I, _P, _P, _P, _P, _P],
     "hfee_sample_chain": [_P, _L, _I, _I, _P, _P, _P, _I, _P, _I, _P, _L, _P, _P, _P],
@@ -73,6 +84,8 @@ def library() -> ctypes.CDLL:
     lib.hfee_set_carveout.argtypes = [_I]
     lib.hfee_gemm_skinny_splits.restype = _I
     lib.hfee_attention_tc_supports.restype = _I
+    lib.hfee_linear_attention_chunked_workspace.restype = _L
+    lib.hfee_linear_attention_chunked_workspace.argtypes = [_I, _I, _I, _I, _I]
     for name, sig in _SIGNATURES.items():
         try:
             fn = getattr(lib, name)
@@ -217,8 +230,8 @@ def _i32(t: Optional[torch.Tensor], what: str) -> None:
 
 # ----------------------------------------------------------------------------
 def embed(table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor, slot_of_token: Optional[torch.Tensor] = None,
-          feedback: Optional[torch.Tensor] = None) -> None:
-    """out[i,:] = table[tokens[i],:] widened to float32.  With ``feedback`` (int32 per request slot)
+          feedback: Optional[torch.Tensor] = None, scale: float = 1.0) -> None:
+    """out[i,:] = table[tokens[i],:] * scale widened to float32.  With ``feedback`` (int32 per request slot)
     a negative token id stands for ``feedback[slot_of_token[i]]``: the token last sampled on the
     device for that request."""
     lib = library()
@@ -227,7 +240,7 @@ def embed(table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor, slot_of_
     assert feedback is None or slot_of_token is not None
     n, width = out.shape
     _check(lib.hfee_embed(table.data_ptr(), _dt(table), tokens.data_ptr(), _ptr(slot_of_token), _ptr(feedback),
-                          out.data_ptr(), n, width, table.shape[0], _stream()), lib)
+                          out.data_ptr(), n, width, table.shape[0], float(scale), _stream()), lib)
 
 
 def rmsnorm(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, eps: float,
@@ -617,6 +630,15 @@ def linear_swiglu(a: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor, g
         swiglu(scratch, out, granule)
 
 
+def linear_gated_normed(inp, w_gate_up: torch.Tensor, out: torch.Tensor, granule: int, scratch: torch.Tensor,
+                        activation: str) -> None:
+    """out = act(a @ w_gate^T) * (a @ w_up^T) for an activation other than SiLU: the projection goes to
+    ``scratch`` [m, 2*inner] and :func:`gated_act` applies the gate."""
+    a = inp if isinstance(inp, torch.Tensor) else inp.tensor()
+    linear(a, w_gate_up, scratch)
+    gated_act(scratch, out, activation, granule)
+
+
 def attention_simt(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, block_table: torch.Tensor,
                    page_size: int, positions: torch.Tensor, slot_of_token: torch.Tensor, out: torch.Tensor,
                    heads: int, kv_heads: int, head_dim: int, scale: float, window: int = 0) -> None:
@@ -779,6 +801,175 @@ def paged_attention_rope(qkv, cs, rope_dim, interleaved, write_cache, k_pool, v_
         count_launches(1)
 
 
+# ---------------------------------------------------------------------------- mechanisms beside softmax attention
+WEIGHTS_SOFTMAX, WEIGHTS_SIGMOID = 0, 1
+ACTIVATIONS = {"none": 0, "silu": 1}
+GATE_ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}
+
+
+def attention_simt_masked(q, k_pool, v_pool, block_table, page_size, positions, slot_of_token, out, heads, kv_heads,
+                          head_dim, scale, window=0, chunk=0, weights=WEIGHTS_SOFTMAX, head_scale=None, head_bias=None,
+                          gate=None) -> None:
+    """:func:`attention_simt` with its options: ``chunk`` > 0 lets a query see only keys of its own block of
+    ``chunk`` positions (counted from position 0 of the request); ``weights`` = WEIGHTS_SIGMOID replaces the
+    softmax by unnormalised weights sigmoid(score * head_scale[h] + head_bias[h]); ``gate`` [n, heads * head_dim]
+    multiplies the output by sigmoid(gate) element by element.  float32 arithmetic in both dtypes."""
+    lib = library()
+    _i32(positions, "positions"); _i32(slot_of_token, "slot_of_token"); _i32(block_table, "block_table")
+    n = q.shape[0]
+    assert q.shape[1] == heads * head_dim and out.shape == q.shape and q.dtype == k_pool.dtype == out.dtype
+    assert k_pool.is_contiguous() and v_pool.is_contiguous()
+    assert tuple(k_pool.shape[1:]) == (kv_heads, page_size, head_dim)
+    for t in (head_scale, head_bias):
+        assert t is None or (t.dtype == torch.float32 and t.is_contiguous() and t.numel() == heads)
+    assert gate is None or (gate.dtype == q.dtype and gate.shape == q.shape)
+    _check(lib.hfee_attention_simt_masked(q.data_ptr(), _rows(q, "q"), k_pool.data_ptr(), v_pool.data_ptr(),
+                                          block_table.data_ptr(), block_table.shape[1], page_size, positions.data_ptr(),
+                                          slot_of_token.data_ptr(), out.data_ptr(), _rows(out, "attention out"), n, heads,
+                                          kv_heads, head_dim, float(scale), int(window or 0), int(chunk or 0), int(weights),
+                                          _ptr(head_scale), _ptr(head_bias), _ptr(gate),
+                                          _rows(gate, "gate") if gate is not None else 0, _dt(q), _stream()), lib)
+
+
+def short_conv(x: torch.Tensor, weight: torch.Tensor, state: torch.Tensor, step, out: torch.Tensor,
+               write_state: bool = True) -> None:
+    """out[t] = x[t] + sum_j weight[:, j] * x[t - taps + 1 + j] per request of the step, inputs in front of the
+    step's tokens taken from ``state`` [slots, taps - 1, width] (float32), which then takes the request's last
+    taps - 1 inputs.  ``x`` is float32 [n, width]; ``out`` may be float32 or bfloat16."""
+    lib = library()
+    n, width = x.shape
+    taps = weight.shape[1]
+    assert x.dtype == torch.float32 and x.is_contiguous() and weight.dtype == torch.float32 and weight.is_contiguous()
+    assert weight.shape[0] == width and state.dtype == torch.float32 and state.is_contiguous()
+    assert tuple(state.shape[1:]) == (taps - 1, width) and out.shape == x.shape
+    _check(lib.hfee_short_conv(x.data_ptr(), weight.data_ptr(), state.data_ptr(), step.cu_tokens.data_ptr(),
+                               step.slots.data_ptr(), out.data_ptr(), _rows(out, "conv out"), _dt(out), step.r,
+                               step.max_new, width, taps, int(write_state), _stream()), lib)
+    if lib.hfee_short_conv_launches(step.max_new, taps, int(write_state)) > 1:
+        count_launches(1)
+
+
+# Prompt portions of at least this many tokens (the longest of the step) take the chunked kernels.
+LINEAR_ATTENTION_CHUNKED_MIN = 8
+
+
+def linear_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay: torch.Tensor, state: torch.Tensor,
+                     step, out: torch.Tensor, heads: int, dim: int, vdim: int, activation: str = "none",
+                     write_state: bool = True, workspace: Optional[torch.Tensor] = None,
+                     chunked: Optional[bool] = None) -> None:
+    """Linear attention with a decay per head over the step's tokens, continuing each request's float32 state
+    ``state`` [slots, heads, dim, vdim]: S <- decay_h S + k v^T, o = S^T q.  ``q``, ``k``, ``v`` are column
+    slices of one projection buffer (same row stride); ``activation`` is applied to them on the way in;
+    ``out`` is float32 [n, heads * vdim].  Steps with a portion of several tokens take the chunked kernels
+    when ``workspace`` (float32, see :func:`linear_attention_workspace`) is given, else the token-by-token one."""
+    lib = library()
+    n = q.shape[0]
+    assert q.dtype == k.dtype == v.dtype and q.stride(0) == k.stride(0) == v.stride(0) and q.stride(1) == 1
+    assert q.shape[1] == k.shape[1] == heads * dim and v.shape[1] == heads * vdim
+    assert decay.dtype == torch.float32 and decay.numel() == heads and state.dtype == torch.float32 and state.is_contiguous()
+    assert tuple(state.shape[1:]) == (heads, dim, vdim) and out.dtype == torch.float32 and out.shape == (n, heads * vdim)
+    act = ACTIVATIONS[activation]
+    if chunked is None:
+        chunked = workspace is not None and step.max_new >= LINEAR_ATTENTION_CHUNKED_MIN
+    if chunked:
+        need = lib.hfee_linear_attention_chunked_workspace(step.r, step.n, heads, dim, vdim)
+        assert workspace is not None and workspace.dtype == torch.float32 and workspace.numel() >= need, (need,)
+        _check(lib.hfee_linear_attention_chunked(q.data_ptr(), k.data_ptr(), v.data_ptr(), q.stride(0), _dt(q),
+                                                 decay.data_ptr(), state.data_ptr(), step.cu_tokens.data_ptr(),
+                                                 step.slots.data_ptr(), out.data_ptr(), _rows(out, "out"),
+                                                 workspace.data_ptr(), workspace.numel(), step.r, step.n, heads,
+                                                 dim, vdim, act, int(write_state), _stream()), lib)
+        count_launches(2)
+        return
+    _check(lib.hfee_linear_attention(q.data_ptr(), k.data_ptr(), v.data_ptr(), q.stride(0), _dt(q), decay.data_ptr(),
+                                     state.data_ptr(), step.cu_tokens.data_ptr(), step.slots.data_ptr(), out.data_ptr(),
+                                     _rows(out, "out"), step.r, heads, dim, vdim, act, int(write_state), _stream()), lib)
+
+
+def linear_attention_workspace(requests: int, tokens: int, heads: int, dim: int, vdim: int) -> int:
+    """Floats of workspace the chunked linear attention needs for a step of ``tokens`` tokens in ``requests`` requests."""
+    return int(library().hfee_linear_attention_chunked_workspace(requests, tokens, heads, dim, vdim))
+
+
+def sigmoid_attention(q, k_pool, v_pool, block_table, page_size, step, out, heads, kv_heads, head_dim, scale, window=0,
+                      chunk=0, head_scale=None, head_bias=None, gate=None) -> None:
+    """Attention with unnormalised sigmoid weights over the cache, choosing the kernel for the dtype and the batch."""
+    attention_simt_masked(q, k_pool, v_pool, block_table, page_size, step.positions, step.slot_of_token, out, heads,
+                          kv_heads, head_dim, scale, window, chunk, WEIGHTS_SIGMOID, head_scale, head_bias, gate)
+
+
+def rmsnorm_add(y: torch.Tensor, weight: torch.Tensor, residual: torch.Tensor, eps: float, add_unit: bool = False) -> None:
+    """residual += y * rsqrt(mean(y^2) + eps) * weight, all float32."""
+    lib = library()
+    assert y.dtype == residual.dtype == weight.dtype == torch.float32 and residual.is_contiguous()
+    n, width = residual.shape
+    assert y.shape == residual.shape and weight.numel() == width
+    _check(lib.hfee_rmsnorm_add(y.data_ptr(), _rows(y, "y"), weight.data_ptr(), residual.data_ptr(), n, width,
+                                float(eps), int(add_unit), _stream()), lib)
+
+
+def norm_gate(x: torch.Tensor, weight: Optional[torch.Tensor], eps: float, gate: torch.Tensor, out: torch.Tensor) -> None:
+    """out = (x * rsqrt(mean(x^2) + eps) * weight) * sigmoid(gate); without ``weight`` only the gate.
+    ``x`` is float32; ``gate`` and ``out`` share a dtype."""
+    lib = library()
+    n, width = x.shape
+    assert x.dtype == torch.float32 and gate.dtype == out.dtype and gate.shape == x.shape == out.shape
+    assert weight is None or (weight.dtype == torch.float32 and weight.numel() == width)
+    _check(lib.hfee_norm_gate(x.data_ptr(), _rows(x, "x"), _ptr(weight), float(eps), gate.data_ptr(), _rows(gate, "gate"),
+                              out.data_ptr(), _rows(out, "out"), n, width, _dt(out), _stream()), lib)
+
+
+def gated_act(gate_up: torch.Tensor, out: torch.Tensor, activation: str, granule: Optional[int] = None) -> None:
+    """out[i, c] = act(gate) * up with the column layout of :func:`swiglu`; ``activation`` is ``"silu"`` or
+    ``"gelu_tanh"`` (0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))))."""
+    lib = library()
+    n, inter = out.shape
+    assert gate_up.shape[1] == 2 * inter and gate_up.dtype == out.dtype
+    _check(lib.hfee_gated_act(gate_up.data_ptr(), _rows(gate_up, "gate_up"), out.data_ptr(), _rows(out, "out"), n, inter,
+                              int(granule or inter), GATE_ACTIVATIONS[activation], _dt(out), _stream()), lib)
+
+
+def scale_(x: torch.Tensor, alpha: float) -> None:
+    """x *= alpha (float32, rows contiguous)."""
+    lib = library()
+    assert x.dtype == torch.float32 and x.dim() == 2
+    _check(lib.hfee_scale_f32(x.data_ptr(), _rows(x, "x"), x.shape[0], x.shape[1], float(alpha), _stream()), lib)
+
+
+def cast_rows(x: torch.Tensor, out: torch.Tensor) -> None:
+    """out = x (float32, contiguous) rounded to ``out``'s dtype."""
+    lib = library()
+    assert x.dtype == torch.float32 and x.is_contiguous() and out.shape == x.shape
+    _check(lib.hfee_cast_rows(x.data_ptr(), out.data_ptr(), _rows(out, "out"), x.shape[0], x.shape[1], _dt(out), _stream()), lib)
+
+
+def qk_norm_rope_cache(qk: torch.Tensor, q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor], eps: float,
+                       cs: Optional[torch.Tensor], rope_dim: int, positions: torch.Tensor, slot_of_token: torch.Tensor,
+                       q_out: torch.Tensor, k_pool: Optional[torch.Tensor], v_pool: Optional[torch.Tensor],
+                       block_table: torch.Tensor, page_size: int, heads: int, kv_heads: int, head_dim: int,
+                       v_offset: int = -1) -> None:
+    """Rows of ``qk`` are [query projection | key projection].  Each is RMS-normed as a whole (all heads at
+    once, weights ``q_weight`` / ``k_weight``; None = no norm), then the first ``rope_dim`` dimensions of every
+    head are rotated (dimension i with i + rope_dim/2) by the step's (cos, sin) table ``cs``.  Queries go to
+    ``q_out``, keys to their cache page, and the value page (if given) takes the key projection as it came
+    (``v_offset`` < 0) or the ``kv_heads * head_dim`` columns of the row that start at ``v_offset``."""
+    lib = library()
+    _i32(positions, "positions"); _i32(slot_of_token, "slot_of_token"); _i32(block_table, "block_table")
+    n = qk.shape[0]
+    want = (heads + kv_heads) * head_dim if k_pool is not None else heads * head_dim
+    assert qk.shape[1] >= max(want, v_offset + kv_heads * head_dim) and q_out.dtype == qk.dtype and q_out.shape == (n, heads * head_dim)
+    if k_pool is not None:
+        assert k_pool.dtype == qk.dtype and k_pool.is_contiguous()
+        assert tuple(k_pool.shape[1:]) == (kv_heads, page_size, head_dim)
+        assert v_pool is None or (v_pool.dtype == qk.dtype and v_pool.is_contiguous() and v_pool.shape == k_pool.shape)
+    assert cs is None or (cs.dtype == torch.float32 and cs.is_contiguous() and cs.numel() == n * rope_dim)
+    _check(lib.hfee_qk_norm_rope_cache(qk.data_ptr(), _rows(qk, "qk"), _ptr(q_weight), _ptr(k_weight), float(eps), _ptr(cs),
+                                       int(rope_dim) if cs is not None else 0, positions.data_ptr(), slot_of_token.data_ptr(),
+                                       q_out.data_ptr(), _rows(q_out, "q_out"), _ptr(k_pool), _ptr(v_pool),
+                                       block_table.data_ptr(), block_table.shape[1], page_size, n, heads, kv_heads,
+                                       head_dim, int(v_offset), _dt(qk), _stream()), lib)
+
+
 def sample(logits: torch.Tensor, out: torch.Tensor, temperature: Optional[torch.Tensor] = None,
            uniform: Optional[torch.Tensor] = None, slots: Optional[torch.Tensor] = None,
            feedback: Optional[torch.Tensor] = None) -> None:
@@ -859,7 +1050,8 @@ def argmax(logits: torch.Tensor, out: torch.Tensor, scratch: torch.Tensor, slots
 
 
 # the entry points the parts and the sampler launch through can be left out by class (see tag())
-for _name in ("embed", "rmsnorm", "rope_table", "rope_cache_write", "swiglu", "linear", "linear_normed", "linear_swiglu", "linear_rope_cache",
+for _name in ("attention_simt_masked", "short_conv", "linear_attention", "rmsnorm_add", "norm_gate", "gated_act", "scale_", "cast_rows",
+              "qk_norm_rope_cache", "embed", "rmsnorm", "rope_table", "rope_cache_write", "swiglu", "linear", "linear_normed", "linear_swiglu", "linear_rope_cache",
               "linear_swiglu_normed", "paged_attention", "paged_attention_rope", "sample", "argmax", "sample_chain"):
     globals()[_name] = _measurable(globals()[_name])
 del _name

@@ -12,6 +12,7 @@ Categories and what each must provide:
 ``mixer``         ``cache_need()`` and ``forward(xn[n,w], residual_f32[n,w], step, cache, writes_cache)``
                   (adds its output into ``residual``)
 ``feed_forward``  ``forward(xn[n,w], residual_f32[n,w], step)`` (adds into ``residual``)
+``conv``          ``cache_need()`` (its history per request) and ``forward(x_f32[n,w], out[n,w], step, state)``
 ``block``         ``forward(residual_f32[n,w], step, cache, writes_cache)``, arranging the above; it is
                   built with ``parts={key: part}`` for the keys its layer spec names
 ``embedding``     ``forward(step, residual_f32[n,w])``
@@ -33,7 +34,7 @@ import torch
 from ..config.spec import PartSpec
 from ..weights.loader import TensorNeed
 
-CATEGORIES = ("norm", "position", "mixer", "feed_forward", "block", "embedding", "head")
+CATEGORIES = ("norm", "position", "mixer", "feed_forward", "conv", "block", "embedding", "head")
 _PARTS: Dict[Tuple[str, str], Type["Part"]] = {}
 
 
@@ -120,7 +121,8 @@ class Block(Part):
         self.parts = dict(parts)
 
     def cache_need(self):
-        """What the layer caches per request: its mixer's need, if it has a part called ``mixer``."""
+        """What the layer caches per request: its mixer's need, if it has a part called ``mixer``.  A block
+        with more than one stateful part returns a :class:`~hfee_b200.cache.CacheBundle`."""
         mixer = self.parts.get("mixer")
         return mixer.cache_need() if mixer is not None else None
 

@@ -5,6 +5,7 @@ from typing import Any
 
 import torch
 
+from ..kernels import ops
 from .base import Block, register_part
 from .norm import LazyNormed
 
@@ -35,4 +36,68 @@ class PreNormBlock(Block):
         return lazy if getattr(consumer, "accepts_lazy_input", False) else lazy.tensor()
 
 
+class OutputNormBlock(Block):
+    """``x += norm(mixer(conv_in(x))); x += norm(feed_forward(x))``: the norms sit on the sublayers'
+    outputs and the sublayers read the residual stream itself.  Optional parts: ``mixer_conv`` (a short
+    convolution over time added to what the mixer reads: the mixer gets ``x + conv(x)``), ``ffn`` with
+    ``ffn_norm`` (a layer may have no feed-forward).  The layer's cache is a bundle: the mixer's pages
+    or its state (named ``recurrent``) and the convolution's history (``conv``)."""
+    needs = ("mixer", "mixer_norm")
+    graph_safe = True
+
+    def __init__(self, spec, tensors, rt, parts):
+        super().__init__(spec, tensors, rt, parts)
+        self.mixer, self.mixer_norm = parts["mixer"], parts["mixer_norm"]
+        self.conv = parts.get("mixer_conv")
+        self.feed_forward, self.ffn_norm = parts.get("ffn"), parts.get("ffn_norm")
+        if (self.feed_forward is None) != (self.ffn_norm is None):
+            raise ValueError("a feed-forward and its output norm come together")
+        self.width = int(spec.width)
+
+    def cache_need(self):
+        from ..cache.needs import CacheBundle, FixedState, PagedKV
+        need = self.mixer.cache_need()
+        if self.conv is None:
+            return need
+        states = {"conv": self.conv.cache_need()}
+        if isinstance(need, FixedState):
+            states["recurrent"] = need
+        elif need is not None and not isinstance(need, PagedKV):
+            raise TypeError(f"an output-norm block cannot bundle a mixer cache of type {type(need).__name__}")
+        return CacheBundle.of(need if isinstance(need, PagedKV) else None, **states)
+
+    def forward(self, residual: torch.Tensor, step: Any, cache: Any, writes_cache: bool) -> None:
+        rt, n = self.rt, step.n
+        y = rt.scratch("block_sublayer_out", (rt.max_tokens, self.width), torch.float32)[:n]
+        if self.conv is not None:
+            h = rt.scratch("block_normed", (rt.max_tokens, self.width))[:n]
+            self.conv.forward(residual, h, step, cache.states["conv"], writes_cache)
+        else:
+            h = self._as_input(residual, n)
+        self._run(self.mixer, y, h, step, cache, writes_cache)
+        self.mixer_norm.forward_add(y, residual)
+        if self.feed_forward is not None:
+            self._run(self.feed_forward, y, self._as_input(residual, n), step)
+            self.ffn_norm.forward_add(y, residual)
+
+    def _as_input(self, residual: torch.Tensor, n: int) -> torch.Tensor:
+        """The residual stream in the dtype the matrix products read."""
+        if self.rt.dtype == torch.float32:
+            return residual
+        x = self.rt.scratch("block_normed", (self.rt.max_tokens, self.width))[:n]
+        ops.tag("norm")
+        ops.cast_rows(residual, x)
+        return x
+
+    @staticmethod
+    def _run(part, y, x, step, *cache_args):
+        """``y = part(x)``: parts that can store their output do; others add into a cleared buffer."""
+        if getattr(part, "can_overwrite", False):
+            part.forward(x, y, step, *cache_args, accumulate=False)
+        else:
+            y.zero_()
+            part.forward(x, y, step, *cache_args)
+
+
 register_part("block", "pre_norm", PreNormBlock)
+register_part("block", "output_norm", OutputNormBlock)

@@ -12,8 +12,8 @@ from .base import Part, register_part
 
 
 class TokenEmbedding(Part):
-    """``x[i,:] = table[token_i,:]``, unscaled (hostfog/hfee internal/llm/forward.go:75-77).
-    spec: ``vocab``, ``width``."""
+    """``x[i,:] = table[token_i,:] * scale`` (hostfog/hfee internal/llm/forward.go:75-77 has no scale).
+    spec: ``vocab``, ``width``, ``scale`` (default 1)."""
     category = "embedding"
     graph_safe = True
 
@@ -24,15 +24,18 @@ class TokenEmbedding(Part):
     def __init__(self, spec, tensors, rt):
         super().__init__(spec, tensors, rt)
         self.table = tensors["table"]
+        self.scale = float(spec.get("scale", 1.0))
 
     def forward(self, step: Any, residual: torch.Tensor) -> None:
         ops.tag("embed")
-        ops.embed(self.table, step.token_ids, residual, step.slot_of_token, getattr(step, "feedback", None))
+        ops.embed(self.table, step.token_ids, residual, step.slot_of_token, getattr(step, "feedback", None),
+                  scale=self.scale)
 
 
 class LinearHead(Part):
-    """``logits = x . W^T`` in float32 (internal/llm/forward.go:132-141).  spec: ``vocab``,
-    ``width``, ``tied`` (use the embedding table as W, internal/llm/model.go:118-121)."""
+    """``logits = x . W^T * scale`` in float32 (internal/llm/forward.go:132-141).  spec: ``vocab``,
+    ``width``, ``tied`` (use the embedding table as W, internal/llm/model.go:118-121), ``scale``
+    (default 1: no scaling pass)."""
     category = "head"
     graph_safe = True
 
@@ -52,6 +55,7 @@ class LinearHead(Part):
             self.weight = embedding.table
         else:
             raise ValueError("the head has no weight and is not tied to the embedding")
+        self.scale = float(spec.get("scale", 1.0))
 
     accepts_lazy_input = True        # the final norm may be fused into the product
 
@@ -62,6 +66,8 @@ class LinearHead(Part):
         else:
             ops.tag("head")
             ops.linear_normed(xn, self.weight, logits)
+        if self.scale != 1.0:
+            ops.scale_(logits, self.scale)
 
 
 register_part("embedding", "token", TokenEmbedding)

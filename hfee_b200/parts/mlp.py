@@ -1,5 +1,6 @@
-"""Dense gated feed-forward: ``down(silu(gate(x)) * up(x))`` added to the residual
-stream (hostfog/hfee internal/llm/forward.go:110-114, internal/ggml/ops.go:160-165)."""
+"""Dense gated feed-forward: ``down(act(gate(x)) * up(x))`` added to the residual
+stream; ``act`` is SiLU (hostfog/hfee internal/llm/forward.go:110-114, internal/ggml/ops.go:160-165)
+or the tanh form of GELU."""
 from __future__ import annotations
 
 from typing import Any, Dict
@@ -13,7 +14,9 @@ from .base import Part, register_part
 
 
 class SwiGLUFeedForward(Part):
-    """spec: ``width``, ``inner`` (intermediate size)."""
+    """spec: ``width``, ``inner`` (intermediate size), ``activation`` (``"silu"``, the default, or
+    ``"gelu_tanh"``).  ``forward(..., accumulate=False)`` stores the output instead of adding it."""
+    can_overwrite = True
     category = "feed_forward"
     graph_safe = True
     accepts_lazy_input = True        # the input norm may be fused into the gate/up projection
@@ -26,6 +29,9 @@ class SwiGLUFeedForward(Part):
     def __init__(self, spec, tensors, rt):
         super().__init__(spec, tensors, rt)
         self.inner = int(spec.inner)
+        self.activation = str(spec.get("activation", "silu"))
+        if self.activation not in ops.GATE_ACTIVATIONS:
+            raise ValueError(f"unknown feed-forward activation {self.activation!r} (known: {sorted(ops.GATE_ACTIVATIONS)})")
         # one fused projection.  bfloat16: rows in groups of 4 gate rows then 4 up rows, so a
         # kernel that owns 8 consecutive rows can apply SwiGLU in its epilogue; else [gate | up].
         gate, up = tensors["gate"], tensors["up"]
@@ -39,14 +45,18 @@ class SwiGLUFeedForward(Part):
             self.w_gate_up = torch.cat([gate, up], dim=0).contiguous()
         self.w_down = tensors["down"]
 
-    def forward(self, xn: torch.Tensor, residual: torch.Tensor, step: Any) -> None:
+    def forward(self, xn: torch.Tensor, residual: torch.Tensor, step: Any, accumulate: bool = True) -> None:
         n, rt = step.n, self.rt
         gu = rt.scratch("ffn_gate_up", (rt.max_tokens, 2 * self.inner))[:n]
         h = rt.scratch("ffn_hidden", (rt.max_tokens, self.inner))[:n]
         ops.tag("gate_up")
-        ops.linear_swiglu_normed(xn, self.w_gate_up, h, self.granule, gu)
+        if self.activation == "silu":
+            ops.linear_swiglu_normed(xn, self.w_gate_up, h, self.granule, gu)
+        else:
+            ops.linear_gated_normed(xn, self.w_gate_up, h, self.granule, gu, self.activation)
         ops.tag("down")
-        ops.linear(h, self.w_down, residual, accumulate=True)
+        ops.linear(h, self.w_down, residual, accumulate=accumulate)
 
 
 register_part("feed_forward", "swiglu", SwiGLUFeedForward)
+register_part("feed_forward", "gated", SwiGLUFeedForward)       # the same part named for its general form

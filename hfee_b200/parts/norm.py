@@ -34,6 +34,12 @@ class RMSNorm(Part):
         ops.tag(before)
 
 
+    def forward_add(self, y: torch.Tensor, residual: torch.Tensor) -> None:
+        """``residual += norm(y)``: the norm on a sublayer's output (both float32)."""
+        before = ops.tag("norm")
+        ops.rmsnorm_add(y, self.weight, residual, self.eps, add_unit=self.add_unit)
+        ops.tag(before)
+
     def fused_params(self):
         """(weight, eps, add_unit): what a kernel needs to apply this norm itself."""
         return self.weight, self.eps, self.add_unit
