@@ -16,6 +16,9 @@ than the 126 MB L2, so no L2 flush is needed between steps.
 
 ``--shape 8b`` / ``13b`` run the layer sizes of Llama-3.1-8B / Llama-2-13B (by default with fewer
 layers, named beside the full number in ``config``), ``--dtype float32`` the true 32-bit path.
+``--design dobelix`` prints, instead of the line above, prompt and decode times of a Dobelix model (linear
+attention with decay, chunked sigmoid attention, short convolutions, norms on the sublayers' outputs) beside a
+Llama model of the same width, heads, feed-forward and number of layers, with what each class of kernels costs.
 ``--breakdown`` prints, instead of the line above, what each class of kernels costs inside the decode
 step at batch 1, 8 and 64 and inside the prompt pass: the step is timed again with that class's
 launches left out (results wrong, timing not), and the difference is the class's cost in place.
@@ -149,6 +152,132 @@ def prefill_flops(cfg, layers, t):
     return 2 * t * layers * n["layer_params"] + attn + 2 * n["head_params"]
 
 
+def dobelix_like(model, layers, chunk=128):
+    """A Dobelix configuration of the layer sizes of the Llama configuration ``model``: every third layer
+    chunked sigmoid attention (from the second on), the others linear attention with as many heads."""
+    h, kv, hd = model["num_attention_heads"], model["num_key_value_heads"], model["head_dim"]
+    ff = {"kind": "dense", "ff": model["intermediate_size"]}
+    decay = [1.0 - 2.0 ** (-1 - 7 * i / max(1, h - 1)) for i in range(h)]
+    out = []
+    for i in range(layers):
+        if i % 3 == 1:
+            out.append({"type": "attention", "mlp": ff,
+                        "mixer": {"heads": h, "kv_heads": kv, "dim": hd, "vdim": hd, "mask": {"size": chunk},
+                                  "rot": {"dims": hd, "base": 10000.0}, "scale": hd ** -0.5}})
+        else:
+            out.append({"type": "lightning", "mlp": ff, "mixer": {"heads": h, "dim": hd, "vdim": hd, "decay": decay}})
+    return {"architecture": "Dobelix", "vocab": model["vocab_size"], "width": model["hidden_size"], "layers": out,
+            "norm": {"eps": 1e-5}, "canon": {"taps": 4}, "embedding": {"scale": 1.0}, "logit_scale": 1.0}
+
+
+def design_comparison(args):
+    """Prompt pass and decode step of a Dobelix model and of the Llama model of equal layer sizes, and the cost
+    of each class of kernels inside them (step time minus step time with the class's launches left out)."""
+    import shutil
+    import numpy as np
+    import torch
+    from hfee_b200 import Engine, StepEntry, write_random_model
+    from hfee_b200.kernels import ops
+
+    pk = peaks()
+    base, base_name, _ = SHAPES[args.shape]
+    layers = args.layers or 6
+    base = dict(base, num_hidden_layers=layers, vocab_size=32768, tie_word_embeddings=True,
+                max_position_embeddings=max(base["max_position_embeddings"], 2 * args.prompt))
+    designs = {"llama": base, "dobelix": dobelix_like(base, layers)}
+    rng = np.random.default_rng(0)
+    out = {"design_comparison": f"{base_name} layer sizes, {layers} layers, vocabulary 32768, bf16, random weights",
+           "prompt_tokens": args.prompt, "decode_batch": args.batch,
+           "classes": "us per layer that has the class: step time minus step time with the class left out"}
+    clocks = ClockSampler()
+    clocks.start()
+    for name, cfg in designs.items():
+        tmp = tempfile.mkdtemp(prefix="hfee_bench_")
+        write_random_model(tmp, cfg, seed=0, dtype="bfloat16")
+        engine = Engine(tmp, dtype=args.dtype, page_size=64, max_requests=args.batch, max_context=2 * args.prompt,
+                        max_batch_tokens=args.prompt, max_cache_tokens=args.batch * 2 * args.prompt,
+                        use_cuda_graphs=not args.no_graphs)
+        shutil.rmtree(tmp, ignore_errors=True)
+        runner = engine.runner
+        vocab = 32768
+
+        def timed(fn, iters):
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for i in range(iters):
+                fn(i)
+            b.record()
+            torch.cuda.synchronize()
+            return a.elapsed_time(b) / iters
+
+        def prefill_ms(tokens, iters=3):
+            prompt = rng.integers(0, vocab, size=tokens).tolist()
+
+            def once(_):
+                s = runner.open()
+                runner.step([StepEntry(s, prompt, [tokens - 1])])
+                runner.close(s)
+            for _ in range(3):
+                once(0)
+            return timed(once, iters)
+
+        def decode_ms(batch, steps=48):
+            slots = [runner.open() for _ in range(batch)]
+            for s in slots:
+                runner.step([StepEntry(s, rng.integers(0, vocab, size=args.prompt).tolist(), [])])
+            feed = rng.integers(0, vocab, size=(steps + 4, batch)).tolist()
+            one = lambda i: runner.step([StepEntry(s, [feed[i][j]], [0]) for j, s in enumerate(slots)])
+            for i in range(4):
+                one(i)
+            ms = timed(lambda i: one(4 + i), steps)
+            for s in slots:
+                runner.close(s)
+            return ms
+
+        def forget_graphs():
+            runner._graphs.clear()
+            runner._graph_seen.clear()
+
+        kinds = [l["type"] for l in cfg["layers"]] if name == "dobelix" else ["attention"] * layers
+        having = {"conv": layers if name == "dobelix" else 0, "gate": kinds.count("lightning") if name == "dobelix" else 0,
+                  "rope": kinds.count("attention")}
+
+        def classes_of(measure, rounds=3):
+            res = {}
+            for c in ("conv", "norm", "qkv", "rope", "attention", "gate", "o", "gate_up", "down", "head"):
+                n = having.get(c, 1 if c == "head" else layers)
+                if n == 0:
+                    continue
+                diffs = []
+                for _ in range(rounds):
+                    ops.leave_out([])
+                    forget_graphs()
+                    whole = measure()
+                    ops.leave_out([c])
+                    forget_graphs()
+                    diffs.append(whole - measure())
+                res[c] = round(statistics.median(diffs) * 1e3 / n, 2)
+            ops.leave_out([])
+            forget_graphs()
+            return res
+
+        r = {"prefill_ms": {str(t): round(prefill_ms(t), 3) for t in sorted({512, args.prompt})},
+             "decode_ms": {str(b): round(decode_ms(b), 4) for b in sorted({1, args.batch})}}
+        r["prefill_tok_s"] = round(args.prompt / (r["prefill_ms"][str(args.prompt)] / 1e3), 1)
+        r["decode_tok_s"] = round(args.batch / (r["decode_ms"][str(args.batch)] / 1e3), 1)
+        if not args.no_points:
+            r["prefill_classes_us"] = classes_of(lambda: prefill_ms(args.prompt, 2))
+            r["decode_classes_us"] = classes_of(lambda: decode_ms(args.batch, 32))
+        out[name] = r
+        del engine, runner
+        torch.cuda.empty_cache()
+    out["clocks"] = clocks.summary()
+    out["peaks"] = {k: pk[k] for k in ("hbm_gbs", "bf16_tflops", "source") if k in pk}
+    print(json.dumps(out))
+    return 0
+
+
 def reference_arm():
     print(json.dumps({"impl": "reference", "unavailable":
                       "hostfog/hfee is a Go program with no Python package (pip: 'neither setup.py nor "
@@ -176,9 +305,14 @@ def main():
     ap.add_argument("--prompt", type=int, default=PROMPT,
                     help="tokens of the prompts (other context lengths than the headline's 2,048; the cache holds twice as many per request)")
     ap.add_argument("--no-graphs", action="store_true", help="profiling aid: launch decode kernels one by one")
+    ap.add_argument("--design", default=None, choices=["dobelix"],
+                    help="instead of the bench line: this design beside the Llama model of equal layer sizes "
+                         "(--shape, --layers, --prompt, --batch apply; --no-points skips the cost per class of kernels)")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm()
+    if args.design:
+        return design_comparison(args)
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2

@@ -10,11 +10,11 @@ import math
 import torch
 
 
-def embed(table, tokens, out, slot_of_token=None, feedback=None):
+def embed(table, tokens, out, slot_of_token=None, feedback=None, scale=1.0):
     tok = tokens.long()
     if feedback is not None:
         tok = torch.where(tok < 0, feedback[slot_of_token.long()].long(), tok)
-    out.copy_(table[tok].float())
+    out.copy_(table[tok].float() * scale)
 
 
 def rmsnorm(x, weight, out, eps, rows=None, add_unit=False):

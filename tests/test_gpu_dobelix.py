@@ -1,0 +1,214 @@
+"""The Dobelix decoder on the GPU against the plain implementation of tests/plain_dobelix.py:
+each mixer alone, whole prompts, prefill then token by token, portions down to two tokens,
+mixed batches over few pages and slots, edges of chunks and pages, far keys, long decoding,
+other sizes, and greedy generation through the engine's entry point."""
+import numpy as np
+import pytest
+
+import dobelix_util as du
+import plain_dobelix as plain
+import replay_util as ru
+
+pytestmark = pytest.mark.gpu
+
+# Largest |difference| relative to the largest |logit| of the plain float64 result on the same stored weights.
+# float32: rounding of float32 sums only.  bfloat16: activations between kernels are rounded to 8 bits of
+# mantissa; the largest of tens of thousands of differences is an extreme value, so the root mean square
+# (relative to that of the logits) is held to a quarter of it.
+TOL = {"float32": 1e-4, "bfloat16": 4e-2}
+RMS_TOL = {"float32": 2e-5, "bfloat16": 1e-2}
+
+
+def rms_err(got, ref):
+    got, ref = np.asarray(got, dtype=np.float64), np.asarray(ref, dtype=np.float64)
+    return float(np.sqrt(np.mean((got - ref) ** 2)) / (np.sqrt(np.mean(ref ** 2)) + 1e-30))
+LENGTHS = (5, 17, 33, 100, 1, 71, 40, 9)
+
+
+@pytest.fixture(scope="module")
+def models(tmp_path_factory):
+    out = {}
+    for name, cfg, seed in (("A", du.DOB_A, 3), ("B", du.DOB_B, 4)):
+        d = du.write_model(str(tmp_path_factory.mktemp("dobelix" + name)), cfg, seed)
+        c, w = plain.load(d)
+        seqs = du.sequences(cfg["vocab"], LENGTHS, seed=11)
+        out[name] = (d, cfg, seqs, [plain.forward(c, w, s) for s in seqs])
+    return out
+
+
+def check(got, ref, dtype, what=""):
+    assert sorted(got) == list(range(len(ref)))
+    for i in range(len(ref)):
+        assert got[i].shape == ref[i].shape
+        err, rms = ru.rel_err(got[i], ref[i]), rms_err(got[i], ref[i])
+        assert err < TOL[dtype] and rms < RMS_TOL[dtype], f"{what} request {i}: relative error {err:.3g}, rms {rms:.3g}"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("scheme", ["whole", "prefill_then_decode", "portions", "mixed"])
+def test_replay(models, name, dtype, scheme):
+    d, cfg, seqs, ref = models[name]
+    if scheme == "mixed":
+        steps = ru.mixed(seqs, live=4, seed=2)
+        # the four longest at once need 100+71+40+33 -> 17 pages of 16 with rounding; slots and pages are used again
+        runner = du.make_runner(d, dtype, max_tokens=17 * 16, context=112)
+    else:
+        steps = {"whole": ru.whole, "prefill_then_decode": lambda s: ru.prefill_then_decode(s, tail=20),
+                 "portions": ru.portions}[scheme](seqs)
+        runner = du.make_runner(d, dtype, max_tokens=112, max_requests=1)
+    check(ru.run_in_process(runner, steps), ref, dtype, scheme)
+
+
+def test_batch_of_unequal_requests_equals_each_alone(models):
+    """float32: a row's sums run in one order whatever else is in the batch."""
+    d, cfg, seqs, ref = models["A"]
+    alone = ru.run_in_process(du.make_runner(d, "float32", 112, max_requests=1), ru.whole(seqs))
+    runner = du.make_runner(d, "float32", max_tokens=512, max_requests=8, context=112)
+    steps = [{"entries": [(i, s, list(range(len(s)))) for i, s in enumerate(seqs)], "end": list(range(len(seqs)))}]
+    together = ru.run_in_process(runner, steps)
+    for i in range(len(seqs)):
+        assert ru.rel_err(together[i], alone[i]) < 2e-6
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("layer", [du.lightning(2, 16, 24, (0.8, 0.999)), du.lightning(1, 144, 40, (1.0,)),
+                                   du.attention(4, 1, 16, chunk=8, rot_dims=8, base=100.0, scale=0.5),
+                                   du.attention(3, 3, 24, chunk=7, rot_dims=24, base=10.0, scale=0.3)],
+                         ids=["lightning", "lightning_wide_keys", "attention_gqa", "attention_odd_chunk"])
+def test_each_mixer_alone(tmp_path, layer, dtype):
+    """One layer without feed-forward: whole, and in portions through the cache or state."""
+    cfg = du.config(48, 90, [layer], taps=2, embedding_scale=1.3, logit_scale=0.5)
+    d = du.write_model(str(tmp_path), cfg, seed=7)
+    c, w = plain.load(d)
+    seqs = du.sequences(90, (37, 3, 64), seed=5)
+    ref = [plain.forward(c, w, s) for s in seqs]
+    for steps in (ru.whole(seqs), ru.portions(seqs, sizes=(2, 9, 1, 1, 30, 2))):
+        check(ru.run_in_process(du.make_runner(d, dtype, 64, max_requests=1), steps), ref, dtype)
+
+
+@pytest.mark.parametrize("taps", [1, 2, 5])
+def test_convolution_taps_and_first_tokens(tmp_path, taps):
+    """The first tokens of a sequence see zeros in front of it; a portion of one or two tokens is shorter
+    than the convolution's history."""
+    cfg = du.config(40, 70, [du.lightning(2, 8, 8, (0.5, 0.9), ff=48)], taps=taps)
+    d = du.write_model(str(tmp_path), cfg, seed=9)
+    c, w = plain.load(d)
+    seqs = du.sequences(70, (9, 2, 1, 30), seed=1)
+    ref = [plain.forward(c, w, s) for s in seqs]
+    runner = du.make_runner(d, "float32", 32, max_requests=1)
+    for steps in (ru.whole(seqs), ru.portions(seqs, sizes=(1, 1, 2, 1, 3, 17, 2)), ru.prefill_then_decode(seqs, tail=6)):
+        check(ru.run_in_process(runner, steps), ref, "float32", f"taps={taps}")
+    if taps > 1:        # and the history matters: without it the second token's logits differ
+        w2 = dict(w); w2["l0.canon1"] = np.zeros_like(w["l0.canon1"])
+        assert ru.rel_err(plain.forward(c, w2, seqs[0])[1:], ref[0][1:]) > 100 * TOL["float32"]
+
+
+def _sharpen_attention(tensors):
+    """Weights with which single keys dominate: a strongly negative bias closes every key whose score is
+    not large, and large query and key norms make some scores large."""
+    for name, t in tensors.items():
+        if name.endswith("mix.pb"):
+            t.fill_(-6.0)
+        if name.endswith("mix.temp"):
+            t.fill_(3.0)
+        if name.endswith("mix.q.norm") or name.endswith("mix.k.norm"):
+            t.mul_(2.5)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_chunk_and_page_edges(tmp_path, dtype):
+    """Keys just inside and just outside a chunk, chunks that end inside a page and pages that end inside a
+    chunk, for prompt portions that start at, before and after an edge and for single decoded tokens."""
+    chunk, page = 24, 16
+    cfg = du.config(32, 60, [du.attention(2, 1, 16, chunk=chunk, rot_dims=16, base=30.0, scale=0.4)], taps=1)
+    d = du.write_model(str(tmp_path), cfg, seed=21, edit=_sharpen_attention)
+    c, w = plain.load(d)
+    seq = du.sequences(60, (100,), seed=2)[0]
+    ref = plain.forward(c, w, seq)
+    # the edge shows: with the chunk one position longer, or one shorter, the logits around an edge change
+    for other in (chunk + 1, chunk - 1):
+        c2 = {**c, "layers": [du.attention(2, 1, 16, chunk=other, rot_dims=16, base=30.0, scale=0.4)]}
+        assert ru.rel_err(plain.forward(c2, w, seq)[chunk - 1:chunk + 2], ref[chunk - 1:chunk + 2]) > 5 * TOL[dtype]
+    cuts = [(100,), (chunk, chunk, 100), (chunk - 1, 2, chunk - 1, 2, 100), (chunk + 1, page - 1, 2, 100),
+            (page, page, page, 100), (47,) + (1,) * 53, (23,) + (1,) * 77]
+    for sizes in cuts:
+        steps = ru.portions([seq], sizes=sizes)
+        got = ru.run_in_process(du.make_runner(d, dtype, 112, page_size=page, max_requests=1), steps)
+        assert ru.rel_err(got[0], ref) < TOL[dtype], f"cut {sizes[:5]}"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_far_keys_reach_through_the_state(tmp_path, dtype):
+    """A head that forgets nothing: the first token still shows hundreds of tokens later, after portions,
+    decoded tokens, and a slot that another request used before."""
+    cfg = du.config(32, 50, [du.lightning(2, 16, 16, (1.0, 0.3))], taps=2)
+
+    def loud_first_token(tensors):          # token 0 stands only at the start and writes a large k v^T into the state
+        tensors["embed"][0] *= 8.0
+    d = du.write_model(str(tmp_path), cfg, seed=33, edit=loud_first_token)
+    c, w = plain.load(d)
+    seq = [0] + [1 + t % 49 for t in du.sequences(50, (399,), seed=8)[0]]
+    other = list(seq); other[0] = 1
+    ref, ref_other = plain.forward(c, w, seq), plain.forward(c, w, other)
+    assert ru.rel_err(ref_other[-8:], ref[-8:]) > 5 * TOL[dtype]         # the far token matters
+    runner = du.make_runner(d, dtype, 416, page_size=32, max_requests=1)
+    for s, r in ((other, ref_other), (seq, ref)):                        # the same slot twice: the state is cleared
+        steps = ru.portions([s], sizes=(130, 2, 67, 1, 1, 100, 64)) if s is seq else ru.prefill_then_decode([s], tail=40)
+        got = ru.run_in_process(runner, steps)
+        assert ru.rel_err(got[0], r) < TOL[dtype]
+
+
+def test_values_are_the_keys_before_norm_and_rotation(tmp_path):
+    """The plain implementation with normed or rotated values gives other logits, so the comparison would see it."""
+    cfg = du.config(32, 40, [du.attention(2, 2, 8, chunk=50, rot_dims=8, base=5.0, scale=0.7)], taps=1)
+    d = du.write_model(str(tmp_path), cfg, seed=5)
+    c, w = plain.load(d)
+    seq = du.sequences(40, (30,), seed=3)[0]
+    ref = plain.forward(c, w, seq)
+    w2 = dict(w); w2["l0.mix.k.norm"] = w["l0.mix.k.norm"] * 1.5          # changes the keys, not the values
+    assert ru.rel_err(plain.forward(c, w2, seq), ref) > 1e-3
+    got = ru.run_in_process(du.make_runner(d, "float32", 32, max_requests=1), ru.whole([seq]))
+    assert ru.rel_err(got[0], ref) < TOL["float32"]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding_with_graphs(models, dtype):
+    """300 tokens one by one behind a short prompt, replayed from CUDA graphs, two requests side by side."""
+    d, cfg, _, _ = models["B"]
+    c, w = plain.load(d)
+    seqs = du.sequences(cfg["vocab"], (330, 317), seed=4)
+    ref = [plain.forward(c, w, s) for s in seqs]
+    runner = du.make_runner(d, dtype, 704, page_size=16, max_requests=2, graphs=True, context=352)
+    assert runner.model.graph_safe
+    steps = ru.batched_decode(seqs, tails=[300, 300])
+    got = ru.run_in_process(runner, steps)
+    assert runner.graph_replays > 250
+    check(got, ref, dtype)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_binary(models, tmp_path, dtype):
+    d, cfg, seqs, ref = models["A"]
+    steps = ru.mixed(seqs, live=4, seed=5)
+    got = ru.run_trace_binary(d, dtype, steps, str(tmp_path), max_tokens=5 * 64, vocab=cfg["vocab"])
+    check(got, ref, dtype)
+
+
+def test_greedy_generation_through_the_engine(models):
+    """Engine.generate (scheduler, sampler, pipelined decode) gives the plain implementation's greedy tokens."""
+    from hfee_b200 import Engine, SamplingOptions
+    d, cfg, seqs, _ = models["A"]
+    c, w = plain.load(d)
+    prompts = [seqs[0], seqs[1], seqs[7], seqs[2], seqs[6]]
+
+    def plain_greedy(prompt, n):
+        toks = list(prompt)
+        for _ in range(n):
+            toks.append(int(np.argmax(plain.forward(c, w, toks)[-1])))
+        return toks[len(prompt):]
+
+    want = [plain_greedy(p, 12) for p in prompts]
+    eng = Engine(d, dtype="float32", page_size=16, max_context=128, max_requests=3, max_batch_tokens=48, prefill_chunk=11)
+    got = [r.token_ids for r in eng.generate(prompts, SamplingOptions.greedy(num_predict=12))]
+    assert got == want
