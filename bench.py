@@ -241,11 +241,12 @@ def design_comparison(args):
 
         kinds = [l["type"] for l in cfg["layers"]] if name == "dobelix" else ["attention"] * layers
         having = {"conv": layers if name == "dobelix" else 0, "gate": kinds.count("lightning") if name == "dobelix" else 0,
-                  "rope": kinds.count("attention")}
+                  "linear_attention": kinds.count("lightning") if name == "dobelix" else 0,
+                  "rope": kinds.count("attention"), "attention": kinds.count("attention")}
 
         def classes_of(measure, rounds=3):
             res = {}
-            for c in ("conv", "norm", "qkv", "rope", "attention", "gate", "o", "gate_up", "down", "head"):
+            for c in ("conv", "norm", "qkv", "rope", "attention", "linear_attention", "gate", "o", "gate_up", "down", "head"):
                 n = having.get(c, 1 if c == "head" else layers)
                 if n == 0:
                     continue

@@ -104,6 +104,17 @@ template <typename T> __device__ __forceinline__ T from_f32(float v);
 template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
 template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
 
+// The tanh form of GELU as a gate: 0.5 z (1 + tanh(u)) = z / (1 + exp(-2u)), u = sqrt(2/pi) (z + 0.044715 z^3).
+// Products whose epilogue applies a gated activation take it as epilogue 4 (SiLU is epilogue 2).
+__device__ __forceinline__ float gelu_tanh_gate(float z) {
+  const float u = 0.7978845608028654f * fmaf(0.044715f * z * z, z, z);
+  return z / (1.f + expf(-2.f * u));
+}
+__device__ __forceinline__ float gelu_tanh_gate_fast(float z) {
+  const float u = 0.7978845608028654f * fmaf(0.044715f * z * z, z, z);
+  return __fdividef(z, 1.f + __expf(-2.f * u));
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

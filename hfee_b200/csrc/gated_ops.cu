@@ -28,9 +28,11 @@ __device__ __forceinline__ float block_sum(float v, float* partial) {
 
 __device__ __forceinline__ float sigmoid_f32(float z) { return 1.f / (1.f + expf(-z)); }
 
+template <typename T>
 __global__ void __launch_bounds__(ROW_THREADS)
 rmsnorm_add_kernel(const float* __restrict__ y, long long ld_y, const float* __restrict__ w,
-                   float* __restrict__ residual, int width, float eps, int add_unit) {
+                   float* __restrict__ residual, int width, float eps, int add_unit, T* __restrict__ cast_out,
+                   long long ld_c) {
   __shared__ float partial[ROW_THREADS / 32];
   pdl_wait();
   pdl_launch_dependents();
@@ -39,8 +41,58 @@ rmsnorm_add_kernel(const float* __restrict__ y, long long ld_y, const float* __r
   float ss = 0.f;
   for (int c = threadIdx.x; c < width; c += ROW_THREADS) ss = fmaf(yr[c], yr[c], ss);
   const float scale = 1.0f / sqrtf(block_sum(ss, partial) / (float)width + eps);
-  for (int c = threadIdx.x; c < width; c += ROW_THREADS)
-    rr[c] += yr[c] * scale * (add_unit ? 1.f + w[c] : w[c]);
+  for (int c = threadIdx.x; c < width; c += ROW_THREADS) {
+    const float r = rr[c] + yr[c] * scale * (add_unit ? 1.f + w[c] : w[c]);
+    rr[c] = r;
+    if (cast_out != nullptr) cast_out[(long long)blockIdx.x * ld_c + c] = from_f32<T>(r);
+  }
+}
+
+// The same for widths that are multiples of 4 and at most ROW_THREADS * 4 * NCH: 16-byte accesses, the row of y
+// and of the residual requested at once and kept in registers between the two passes.
+template <typename T, int NCH>
+__global__ void __launch_bounds__(ROW_THREADS)
+rmsnorm_add_vec_kernel(const float* __restrict__ y, long long ld_y, const float* __restrict__ w,
+                       float* __restrict__ residual, int width, float eps, int add_unit, T* __restrict__ cast_out,
+                       long long ld_c) {
+  __shared__ float partial[ROW_THREADS / 32];
+  float4 wv[NCH];
+#pragma unroll
+  for (int j = 0; j < NCH; ++j) {
+    const int c = (threadIdx.x + j * ROW_THREADS) * 4;
+    wv[j] = c < width ? __ldg(reinterpret_cast<const float4*>(w + c)) : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  pdl_wait();
+  pdl_launch_dependents();
+  const float* yr = y + (long long)blockIdx.x * ld_y;
+  float* rr = residual + (long long)blockIdx.x * width;
+  float4 yv[NCH], rv[NCH];
+#pragma unroll
+  for (int j = 0; j < NCH; ++j) {
+    const int c = (threadIdx.x + j * ROW_THREADS) * 4;
+    yv[j] = c < width ? *reinterpret_cast<const float4*>(yr + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+    rv[j] = c < width ? *reinterpret_cast<const float4*>(rr + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  float ss = 0.f;
+#pragma unroll
+  for (int j = 0; j < NCH; ++j) ss = fmaf(yv[j].x, yv[j].x, fmaf(yv[j].y, yv[j].y, fmaf(yv[j].z, yv[j].z, fmaf(yv[j].w, yv[j].w, ss))));
+  const float scale = 1.0f / sqrtf(block_sum(ss, partial) / (float)width + eps);
+  const float unit = add_unit ? 1.f : 0.f;
+#pragma unroll
+  for (int j = 0; j < NCH; ++j) {
+    const int c = (threadIdx.x + j * ROW_THREADS) * 4;
+    if (c >= width) continue;
+    float4 r = rv[j];
+    r.x += yv[j].x * scale * (wv[j].x + unit);
+    r.y += yv[j].y * scale * (wv[j].y + unit);
+    r.z += yv[j].z * scale * (wv[j].z + unit);
+    r.w += yv[j].w * scale * (wv[j].w + unit);
+    *reinterpret_cast<float4*>(rr + c) = r;
+    if (cast_out != nullptr) {
+      T* dst = cast_out + (long long)blockIdx.x * ld_c + c;
+      dst[0] = from_f32<T>(r.x); dst[1] = from_f32<T>(r.y); dst[2] = from_f32<T>(r.z); dst[3] = from_f32<T>(r.w);
+    }
+  }
 }
 
 template <typename T>
@@ -158,11 +210,33 @@ qk_norm_rope_cache_kernel(const T* __restrict__ qk, long long ld_qk, const float
 
 }  // namespace
 
+namespace {
+template <typename T>
+void launch_rmsnorm_add(const float* y, long long ld_y, const float* w, float* residual, int n, int width, float eps,
+                        int add_unit, void* cast_out, long long ld_c, cudaStream_t stream) {
+  const bool vec = width % 4 == 0 && ld_y % 4 == 0 && (uintptr_t)y % 16 == 0 && (uintptr_t)residual % 16 == 0 &&
+                   (uintptr_t)w % 16 == 0;
+  if (vec && width <= ROW_THREADS * 4 * 2)
+    hfee_launch(rmsnorm_add_vec_kernel<T, 2>, dim3(n), dim3(ROW_THREADS), 0, stream, y, ld_y, w, residual, width, eps, add_unit, (T*)cast_out, ld_c);
+  else if (vec && width <= ROW_THREADS * 4 * 8)
+    hfee_launch(rmsnorm_add_vec_kernel<T, 8>, dim3(n), dim3(ROW_THREADS), 0, stream, y, ld_y, w, residual, width, eps, add_unit, (T*)cast_out, ld_c);
+  else
+    hfee_launch(rmsnorm_add_kernel<T>, dim3(n), dim3(ROW_THREADS), 0, stream, y, ld_y, w, residual, width, eps, add_unit, (T*)cast_out, ld_c);
+}
+}  // namespace
+
+// residual += norm(y); with cast_out the new residual row is also written there in the activations' type
 HFEE_API int hfee_rmsnorm_add(const float* y, long long ld_y, const float* w, float* residual, int n, int width,
-                              float eps, int add_unit, cudaStream_t stream) {
+                              float eps, int add_unit, void* cast_out, long long ld_c, int cast_dtype, cudaStream_t stream) {
   if (n == 0) return HFEE_OK;
   HFEE_REQUIRE(n > 0 && width > 0 && ld_y >= width, "rmsnorm_add: bad sizes");
-  hfee_launch(rmsnorm_add_kernel, dim3(n), dim3(ROW_THREADS), 0, stream, y, ld_y, w, residual, width, eps, add_unit);
+  HFEE_REQUIRE(cast_out == nullptr || ld_c >= width, "rmsnorm_add: ld_c=%lld is too small", ld_c);
+  if (cast_out != nullptr && cast_dtype == HFEE_BF16)
+    launch_rmsnorm_add<__nv_bfloat16>(y, ld_y, w, residual, n, width, eps, add_unit, cast_out, ld_c, stream);
+  else if (cast_out == nullptr || cast_dtype == HFEE_F32)
+    launch_rmsnorm_add<float>(y, ld_y, w, residual, n, width, eps, add_unit, cast_out, ld_c, stream);
+  else
+    return hfee_fail(HFEE_ERR_ARG, "rmsnorm_add: unknown dtype %d", cast_dtype);
   return hfee_check_launch("rmsnorm_add");
 }
 

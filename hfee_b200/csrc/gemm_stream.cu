@@ -22,7 +22,7 @@ namespace {
 
 constexpr int LOADS_IN_FLIGHT = 4;   // 16-byte weight loads per lane in one batch; two batches are in flight
 
-enum Epilogue { EPI_STORE = 0, EPI_ACCUM = 1, EPI_SWIGLU = 2 };
+enum Epilogue { EPI_STORE = 0, EPI_ACCUM = 1, EPI_SWIGLU = 2, EPI_GEGLU = 4 };
 
 __device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                          uint32_t b0, uint32_t b1) {
@@ -153,7 +153,7 @@ gemm_stream_kernel(const __nv_bfloat16* __restrict__ A, long long lda, const __n
         for (int i = 0; i < 4; ++i) acc[mt][nt][i] = 0.f;
       }
     __syncthreads();
-    if constexpr (EPI == EPI_SWIGLU) {
+    if constexpr (EPI == EPI_SWIGLU || EPI == EPI_GEGLU) {
       // rows of a group of 8: [gate x4 | up x4] -> 4 outputs at columns (n0/2 + group*4 ..)
       constexpr int OUTS = ROWS / 2;
       for (int idx = threadIdx.x; idx < MT * 16 * OUTS; idx += NW * 32) {
@@ -164,7 +164,7 @@ gemm_stream_kernel(const __nv_bfloat16* __restrict__ A, long long lda, const __n
         float gate = 0.f, up = 0.f;
 #pragma unroll
         for (int w = 0; w < NW; ++w) { gate += red[w][t][gr]; up += red[w][t][gr + 4]; }
-        C[(long long)t * ldc + col] = from_f32<TOut>(gate / (1.f + expf(-gate)) * up);
+        C[(long long)t * ldc + col] = from_f32<TOut>((EPI == EPI_GEGLU ? gelu_tanh_gate(gate) : gate / (1.f + expf(-gate))) * up);
       }
     } else {
       for (int idx = threadIdx.x; idx < MT * 16 * ROWS; idx += NW * 32) {
@@ -272,7 +272,7 @@ gemm_stream_rows_kernel(const __nv_bfloat16* __restrict__ A, long long lda, cons
     const int n0 = (first + tile_no * warps) * 8;
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt) {
-      if constexpr (EPI == EPI_SWIGLU) {
+      if constexpr (EPI == EPI_SWIGLU || EPI == EPI_GEGLU) {
         // rows 0-3 gate, 4-7 up: lanes c = 0,1 hold gate, c = 2,3 the matching up values
         float u0 = __shfl_xor_sync(0xffffffffu, acc[mt][0], 2), u1 = __shfl_xor_sync(0xffffffffu, acc[mt][1], 2);
         float u2 = __shfl_xor_sync(0xffffffffu, acc[mt][2], 2), u3 = __shfl_xor_sync(0xffffffffu, acc[mt][3], 2);
@@ -288,7 +288,7 @@ gemm_stream_rows_kernel(const __nv_bfloat16* __restrict__ A, long long lda, cons
             for (int e = 0; e < 2; ++e) {
               if (col + e >= N / 2) continue;
               float gate = gv[2 * h + e], up = uv[2 * h + e];
-              C[(long long)t * ldc + col + e] = from_f32<TOut>(gate / (1.f + expf(-gate)) * up);
+              C[(long long)t * ldc + col + e] = from_f32<TOut>((EPI == EPI_GEGLU ? gelu_tanh_gate(gate) : gate / (1.f + expf(-gate))) * up);
             }
           }
         }
@@ -464,7 +464,7 @@ gemm_stream_slices_kernel(const __nv_bfloat16* __restrict__ A, long long lda, co
     const int gs = group_size(grp);
     const int t0 = t_begin + grp * SL_GROUP;
     const float (*part)[8][SL_TOKEN_PITCH] = red[grp & 1];
-    if constexpr (EPI == EPI_SWIGLU) {
+    if constexpr (EPI == EPI_SWIGLU || EPI == EPI_GEGLU) {
       // rows of a tile: [gate x4 | up x4] -> 4 outputs at columns tile*4 ..
       const int t = threadIdx.x >> 5, o = threadIdx.x & 31;
       const int tile = o >> 2, i = o & 3;
@@ -473,7 +473,7 @@ gemm_stream_slices_kernel(const __nv_bfloat16* __restrict__ A, long long lda, co
         float gate = 0.f, up = 0.f;
 #pragma unroll
         for (int w = 0; w < SL_WARPS; ++w) { gate += part[w][t][tile * 8 + i]; up += part[w][t][tile * 8 + 4 + i]; }
-        C[(long long)t * ldc + col] = from_f32<TOut>(gate / (1.f + expf(-gate)) * up);
+        C[(long long)t * ldc + col] = from_f32<TOut>((EPI == EPI_GEGLU ? gelu_tanh_gate(gate) : gate / (1.f + expf(-gate))) * up);
       }
     } else {
 #pragma unroll
@@ -579,7 +579,7 @@ gemm_stream_wide_kernel(const __nv_bfloat16* __restrict__ A, long long lda, cons
   auto finish_group = [&](int grp) {
     const int gs = group_size(grp);
     const int t0 = t_begin + grp * SL_GROUP;
-    if constexpr (EPI == EPI_SWIGLU) {
+    if constexpr (EPI == EPI_SWIGLU || EPI == EPI_GEGLU) {
       const int t = threadIdx.x >> 5, o = threadIdx.x & 31;             // 16 tokens x 32 outputs = 512 threads
       const int tile = o >> 2, i = o & 3;
       const long long col = (long long)(t0 + tile) * 4 + i;
@@ -587,7 +587,7 @@ gemm_stream_wide_kernel(const __nv_bfloat16* __restrict__ A, long long lda, cons
         float gate = 0.f, up = 0.f;
 #pragma unroll
         for (int w = 0; w < WD_WARPS; ++w) { gate += red[w][t][tile * 8 + i]; up += red[w][t][tile * 8 + 4 + i]; }
-        C[(long long)t * ldc + col] = from_f32<TOut>(gate / (1.f + expf(-gate)) * up);
+        C[(long long)t * ldc + col] = from_f32<TOut>((EPI == EPI_GEGLU ? gelu_tanh_gate(gate) : gate / (1.f + expf(-gate))) * up);
       }
     } else {
 #pragma unroll
@@ -657,6 +657,8 @@ int launch_wide(const void* A, long long lda, const void* W, long long ldw, void
     HFEE_GO(EPI_ACCUM, float);
   } else if (epilogue == EPI_SWIGLU) {
     if (out_dtype == HFEE_BF16) HFEE_GO(EPI_SWIGLU, __nv_bfloat16); else HFEE_GO(EPI_SWIGLU, float);
+  } else if (epilogue == EPI_GEGLU) {
+    if (out_dtype == HFEE_BF16) HFEE_GO(EPI_GEGLU, __nv_bfloat16); else HFEE_GO(EPI_GEGLU, float);
   } else {
     if (out_dtype == HFEE_BF16) HFEE_GO(EPI_STORE, __nv_bfloat16); else HFEE_GO(EPI_STORE, float);
   }
@@ -679,6 +681,8 @@ int launch_slices(const void* A, long long lda, const void* W, long long ldw, vo
     HFEE_GO(EPI_ACCUM, float);
   } else if (epilogue == EPI_SWIGLU) {
     if (out_dtype == HFEE_BF16) HFEE_GO(EPI_SWIGLU, __nv_bfloat16); else HFEE_GO(EPI_SWIGLU, float);
+  } else if (epilogue == EPI_GEGLU) {
+    if (out_dtype == HFEE_BF16) HFEE_GO(EPI_GEGLU, __nv_bfloat16); else HFEE_GO(EPI_GEGLU, float);
   } else {
     if (out_dtype == HFEE_BF16) HFEE_GO(EPI_STORE, __nv_bfloat16); else HFEE_GO(EPI_STORE, float);
   }
@@ -706,6 +710,8 @@ int launch(const void* A, long long lda, const void* W, long long ldw, void* C, 
     HFEE_GO(EPI_ACCUM, float);
   } else if (epilogue == EPI_SWIGLU) {
     if (out_dtype == HFEE_BF16) HFEE_GO(EPI_SWIGLU, __nv_bfloat16); else HFEE_GO(EPI_SWIGLU, float);
+  } else if (epilogue == EPI_GEGLU) {
+    if (out_dtype == HFEE_BF16) HFEE_GO(EPI_GEGLU, __nv_bfloat16); else HFEE_GO(EPI_GEGLU, float);
   } else {
     if (out_dtype == HFEE_BF16) HFEE_GO(EPI_STORE, __nv_bfloat16); else HFEE_GO(EPI_STORE, float);
   }
@@ -732,6 +738,8 @@ int launch_rows(const void* A, long long lda, const void* W, long long ldw, void
     HFEE_GO(EPI_ACCUM, float);
   } else if (epilogue == EPI_SWIGLU) {
     if (out_dtype == HFEE_BF16) HFEE_GO(EPI_SWIGLU, __nv_bfloat16); else HFEE_GO(EPI_SWIGLU, float);
+  } else if (epilogue == EPI_GEGLU) {
+    if (out_dtype == HFEE_BF16) HFEE_GO(EPI_GEGLU, __nv_bfloat16); else HFEE_GO(EPI_GEGLU, float);
   } else {
     if (out_dtype == HFEE_BF16) HFEE_GO(EPI_STORE, __nv_bfloat16); else HFEE_GO(EPI_STORE, float);
   }
@@ -754,14 +762,14 @@ int check_common(const void* W, long long ldw, long long ldc, int epilogue, int 
   HFEE_REQUIRE(N > 0 && K > 0 && K % 8 == 0, "gemm_stream: K=%d must be a positive multiple of 8", K);
   HFEE_REQUIRE(ldw % 8 == 0 && ldw >= K, "gemm_stream: the weights' leading dimension %lld must be a multiple of 8 and at least K", ldw);
   HFEE_REQUIRE((uintptr_t)W % 16 == 0, "gemm_stream: weights must be 16-byte aligned");
-  HFEE_REQUIRE(epilogue >= 0 && epilogue <= 2, "gemm_stream: unknown epilogue %d", epilogue);
-  HFEE_REQUIRE(epilogue != EPI_SWIGLU || N % 8 == 0, "gemm_stream: SwiGLU needs N %% 8 == 0, got %d", N);
-  HFEE_REQUIRE(ldc >= (epilogue == EPI_SWIGLU ? N / 2 : N), "gemm_stream: ldc=%lld is too small", ldc);
+  HFEE_REQUIRE((epilogue >= 0 && epilogue <= 2) || epilogue == EPI_GEGLU, "gemm_stream: unknown epilogue %d", epilogue);
+  HFEE_REQUIRE((epilogue != EPI_SWIGLU && epilogue != EPI_GEGLU) || N % 8 == 0, "gemm_stream: SwiGLU needs N %% 8 == 0, got %d", N);
+  HFEE_REQUIRE(ldc >= ((epilogue == EPI_SWIGLU || epilogue == EPI_GEGLU) ? N / 2 : N), "gemm_stream: ldc=%lld is too small", ldc);
   return HFEE_OK;
 }
 }  // namespace
 
-// epilogue: 0 store, 1 accumulate into float32 C, 2 SwiGLU (C is [M, N/2]; N % 8 == 0).
+// epilogue: 0 store, 1 accumulate into float32 C, 2 SwiGLU and 4 the same with a tanh-GELU gate (C is [M, N/2]; N % 8 == 0).
 HFEE_API int hfee_gemm_stream(const void* A, long long lda, const void* W, long long ldw, void* C, long long ldc,
                               int out_dtype, int epilogue, int M, int N, int K, cudaStream_t stream) {
   if (M == 0 || N == 0) return HFEE_OK;

@@ -41,7 +41,7 @@ constexpr int EPI_WARPS = 8;
 constexpr int ACC_STAGES = 2;
 constexpr int SK_MAX_PIECES = 4;      // a tile is cut into at most this many ranges of K blocks
 
-enum Epilogue { EPI_STORE = 0, EPI_ACCUM = 1, EPI_SWIGLU = 2, EPI_ROPE = 3 };
+enum Epilogue { EPI_STORE = 0, EPI_ACCUM = 1, EPI_SWIGLU = 2, EPI_ROPE = 3, EPI_GEGLU = 4 };
 
 template <int BN> struct TileCfg {
   static constexpr int STAGES = BN == 128 ? 6 : 4;
@@ -277,7 +277,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           }
         }
         if (row >= M || col0 >= N) continue;
-        if constexpr (EPI == EPI_SWIGLU) {
+        if constexpr (EPI == EPI_SWIGLU || EPI == EPI_GEGLU) {
           // columns in groups of 8 = [4 gate | 4 up] -> 4 outputs per group at column col/2
           TOut* dst = C + (long long)row * ldc + col0 / 2;
           float o[16];
@@ -286,7 +286,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
               float gate = __uint_as_float(v[gq * 8 + i]), up = __uint_as_float(v[gq * 8 + 4 + i]);
-              o[gq * 4 + i] = __fdividef(gate, 1.f + __expf(-gate)) * up;
+              o[gq * 4 + i] = (EPI == EPI_GEGLU ? gelu_tanh_gate_fast(gate) : __fdividef(gate, 1.f + __expf(-gate))) * up;
             }
           if (col0 + 32 <= N && (((uintptr_t)dst) & 15) == 0) {
 #pragma unroll
@@ -449,8 +449,9 @@ int dispatch(const CUtensorMap& ma, const CUtensorMap& mw, void* C, long long ld
     if (out_dtype != HFEE_F32) return hfee_fail(HFEE_ERR_ARG, "gemm_tcgen05: accumulate needs a float32 output");
     return launch<BN, EPI_ACCUM, float>(ma, mw, C, ldc, M, N, K, status, ws, ws_floats, flags, stream);
   }
-  if (epilogue == EPI_SWIGLU) {
-    if (out_dtype != HFEE_BF16) return hfee_fail(HFEE_ERR_ARG, "gemm_tcgen05: the SwiGLU epilogue writes bfloat16");
+  if (epilogue == EPI_SWIGLU || epilogue == EPI_GEGLU) {
+    if (out_dtype != HFEE_BF16) return hfee_fail(HFEE_ERR_ARG, "gemm_tcgen05: the gated epilogues write bfloat16");
+    if (epilogue == EPI_GEGLU) return launch<BN, EPI_GEGLU, __nv_bfloat16>(ma, mw, C, ldc, M, N, K, status, ws, ws_floats, flags, stream);
     return launch<BN, EPI_SWIGLU, __nv_bfloat16>(ma, mw, C, ldc, M, N, K, status, ws, ws_floats, flags, stream);
   }
   if (out_dtype == HFEE_BF16) return launch<BN, EPI_STORE, __nv_bfloat16>(ma, mw, C, ldc, M, N, K, status, ws, ws_floats, flags, stream);
@@ -473,9 +474,9 @@ HFEE_API int hfee_gemm_tcgen05(const void* A, long long lda, const void* W, long
   HFEE_REQUIRE(lda % 8 == 0 && ldw % 8 == 0 && lda >= K && ldw >= K,
                "gemm_tcgen05: leading dimensions (%lld, %lld) must be multiples of 8 and at least K", lda, ldw);
   HFEE_REQUIRE(((uintptr_t)A % 16 == 0) && ((uintptr_t)W % 16 == 0), "gemm_tcgen05: operands must be 16-byte aligned");
-  HFEE_REQUIRE(epilogue >= 0 && epilogue <= 2, "gemm_tcgen05: unknown epilogue %d", epilogue);
-  HFEE_REQUIRE(epilogue != EPI_SWIGLU || N % 8 == 0, "gemm_tcgen05: SwiGLU needs N %% 8 == 0, got %d", N);
-  HFEE_REQUIRE(ldc >= (epilogue == EPI_SWIGLU ? N / 2 : N), "gemm_tcgen05: ldc=%lld is too small", ldc);
+  HFEE_REQUIRE((epilogue >= 0 && epilogue <= 2) || epilogue == EPI_GEGLU, "gemm_tcgen05: unknown epilogue %d", epilogue);
+  HFEE_REQUIRE((epilogue != EPI_SWIGLU && epilogue != EPI_GEGLU) || N % 8 == 0, "gemm_tcgen05: SwiGLU needs N %% 8 == 0, got %d", N);
+  HFEE_REQUIRE(ldc >= ((epilogue == EPI_SWIGLU || epilogue == EPI_GEGLU) ? N / 2 : N), "gemm_tcgen05: ldc=%lld is too small", ldc);
   HFEE_REQUIRE(block_n == 128 || block_n == 192 || block_n == 256, "gemm_tcgen05: block_n must be 128, 192 or 256");
   HFEE_REQUIRE((long long)((M + BM - 1) / BM) * ((N + block_n - 1) / block_n) < (1ll << 31), "gemm_tcgen05: too many tiles");
   CUtensorMap ma, mw;

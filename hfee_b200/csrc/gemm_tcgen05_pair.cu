@@ -40,7 +40,7 @@ template <int BN> struct PairCfg {
   static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 + EPI_BYTES;
 };
 
-enum Epilogue { EPI_STORE = 0, EPI_ACCUM = 1, EPI_SWIGLU = 2, EPI_ROPE = 3 };
+enum Epilogue { EPI_STORE = 0, EPI_ACCUM = 1, EPI_SWIGLU = 2, EPI_ROPE = 3, EPI_GEGLU = 4 };
 
 __device__ __forceinline__ uint32_t cluster_rank() {
   uint32_t r;
@@ -224,7 +224,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           }
         }
         if (row >= M || col0 >= N) continue;
-        if constexpr (EPI == EPI_SWIGLU) {
+        if constexpr (EPI == EPI_SWIGLU || EPI == EPI_GEGLU) {
           // columns in groups of 8 = [4 gate | 4 up] -> 4 outputs per group at column col / 2
           TOut* dst = C + (long long)row * ldc + col0 / 2;
           float o[16];
@@ -233,7 +233,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
               float gate = __uint_as_float(v[gq * 8 + i]), up = __uint_as_float(v[gq * 8 + 4 + i]);
-              o[gq * 4 + i] = __fdividef(gate, 1.f + __expf(-gate)) * up;
+              o[gq * 4 + i] = (EPI == EPI_GEGLU ? gelu_tanh_gate_fast(gate) : __fdividef(gate, 1.f + __expf(-gate))) * up;
             }
           if (col0 + 32 <= N && (((uintptr_t)dst) & 15) == 0) {
 #pragma unroll
@@ -382,9 +382,9 @@ HFEE_API int hfee_gemm_tcgen05_pair(const void* A, long long lda, const void* W,
   HFEE_REQUIRE(lda % 8 == 0 && ldw % 8 == 0 && lda >= K && ldw >= K,
                "gemm_tcgen05_pair: leading dimensions (%lld, %lld) must be multiples of 8 and at least K", lda, ldw);
   HFEE_REQUIRE(((uintptr_t)A % 16 == 0) && ((uintptr_t)W % 16 == 0), "gemm_tcgen05_pair: operands must be 16-byte aligned");
-  HFEE_REQUIRE(epilogue >= 0 && epilogue <= 2, "gemm_tcgen05_pair: unknown epilogue %d", epilogue);
-  HFEE_REQUIRE(epilogue != EPI_SWIGLU || N % 8 == 0, "gemm_tcgen05_pair: SwiGLU needs N %% 8 == 0, got %d", N);
-  HFEE_REQUIRE(ldc >= (epilogue == EPI_SWIGLU ? N / 2 : N), "gemm_tcgen05_pair: ldc=%lld is too small", ldc);
+  HFEE_REQUIRE((epilogue >= 0 && epilogue <= 2) || epilogue == EPI_GEGLU, "gemm_tcgen05_pair: unknown epilogue %d", epilogue);
+  HFEE_REQUIRE((epilogue != EPI_SWIGLU && epilogue != EPI_GEGLU) || N % 8 == 0, "gemm_tcgen05_pair: SwiGLU needs N %% 8 == 0, got %d", N);
+  HFEE_REQUIRE(ldc >= ((epilogue == EPI_SWIGLU || epilogue == EPI_GEGLU) ? N / 2 : N), "gemm_tcgen05_pair: ldc=%lld is too small", ldc);
   CUtensorMap ma, mw;
   int rc = make_map(&ma, A, M, K, lda, BM);
   if (rc != HFEE_OK) return rc;
@@ -394,8 +394,9 @@ HFEE_API int hfee_gemm_tcgen05_pair(const void* A, long long lda, const void* W,
     if (out_dtype != HFEE_F32) return hfee_fail(HFEE_ERR_ARG, "gemm_tcgen05_pair: accumulate needs a float32 output");
     return launch_pair<256, EPI_ACCUM, float>(ma, mw, C, ldc, M, N, K, status, stream);
   }
-  if (epilogue == EPI_SWIGLU) {
-    if (out_dtype != HFEE_BF16) return hfee_fail(HFEE_ERR_ARG, "gemm_tcgen05_pair: the SwiGLU epilogue writes bfloat16");
+  if (epilogue == EPI_SWIGLU || epilogue == EPI_GEGLU) {
+    if (out_dtype != HFEE_BF16) return hfee_fail(HFEE_ERR_ARG, "gemm_tcgen05_pair: the gated epilogues write bfloat16");
+    if (epilogue == EPI_GEGLU) return launch_pair<256, EPI_GEGLU, __nv_bfloat16>(ma, mw, C, ldc, M, N, K, status, stream);
     return launch_pair<256, EPI_SWIGLU, __nv_bfloat16>(ma, mw, C, ldc, M, N, K, status, stream);
   }
   if (out_dtype == HFEE_BF16) return launch_pair<256, EPI_STORE, __nv_bfloat16>(ma, mw, C, ldc, M, N, K, status, stream);

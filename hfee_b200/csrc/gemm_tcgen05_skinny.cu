@@ -22,7 +22,7 @@ constexpr int WM = 128;                 // weight rows per tile
 constexpr int SK_THREADS = 192;         // 1 TMA warp, 1 MMA warp, 4 epilogue warps
 constexpr int ACC_STAGES = 2;
 
-enum Epilogue { EPI_STORE = 0, EPI_ACCUM = 1, EPI_SWIGLU = 2 };
+enum Epilogue { EPI_STORE = 0, EPI_ACCUM = 1, EPI_SWIGLU = 2, EPI_GEGLU = 4 };
 
 template <int TN> struct SkinnyCfg {
   static constexpr int W_BYTES = WM * BK * 2;
@@ -62,7 +62,7 @@ __device__ __forceinline__ void write_columns(const uint32_t (&v)[COLS], int tok
     }
     return;
   }
-  if constexpr (EPI == EPI_SWIGLU) {
+  if constexpr (EPI == EPI_SWIGLU || EPI == EPI_GEGLU) {
     // weight rows come in groups of 8 = [4 gate | 4 up]: the up partner of this lane's row is 4 lanes on
     const bool writer = (lane & 7) < 4 && w_row + 4 < a.N;
     const long long col = (long long)(w_row >> 3) * 4 + (lane & 3);
@@ -74,8 +74,8 @@ __device__ __forceinline__ void write_columns(const uint32_t (&v)[COLS], int tok
         // a bfloat16 result does not need the exact exponential and division (the large-tile kernel
         // computes it the same way)
         float h;
-        if constexpr (sizeof(TOut) == 2) h = __fdividef(gate, 1.f + __expf(-gate)) * up;
-        else h = gate / (1.f + expf(-gate)) * up;
+        if constexpr (sizeof(TOut) == 2) h = (EPI == EPI_GEGLU ? gelu_tanh_gate_fast(gate) : __fdividef(gate, 1.f + __expf(-gate))) * up;
+        else h = (EPI == EPI_GEGLU ? gelu_tanh_gate(gate) : gate / (1.f + expf(-gate))) * up;
         C[(long long)(tok0 + j) * a.ldc + col] = from_f32<TOut>(h);
       }
     }
@@ -240,12 +240,12 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ ws, TOut* __restr
                                      int splits) {
   pdl_wait();
   pdl_launch_dependents();
-  const int out_cols = EPI == EPI_SWIGLU ? N / 2 : N;
+  const int out_cols = (EPI == EPI_SWIGLU || EPI == EPI_GEGLU) ? N / 2 : N;
   long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= (long long)M * out_cols) return;
   const int t = (int)(idx / out_cols), c = (int)(idx % out_cols);
   const long long split_pitch = (long long)M * N;
-  if constexpr (EPI == EPI_SWIGLU) {
+  if constexpr (EPI == EPI_SWIGLU || EPI == EPI_GEGLU) {
     const float* p = ws + (long long)t * N + (c >> 2) * 8 + (c & 3);
     float gate = 0.f, up = 0.f;
     for (int s0 = 0; s0 < splits; s0 += RED_BATCH) {
@@ -259,7 +259,7 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ ws, TOut* __restr
 #pragma unroll
       for (int j = 0; j < RED_BATCH; ++j) { gate += g[j]; up += u[j]; }
     }
-    C[(long long)t * ldc + c] = from_f32<TOut>(gate / (1.f + expf(-gate)) * up);
+    C[(long long)t * ldc + c] = from_f32<TOut>((EPI == EPI_GEGLU ? gelu_tanh_gate(gate) : gate / (1.f + expf(-gate))) * up);
   } else {
     const float* p = ws + (long long)t * N + c;
     const long long o = (long long)t * ldc + c;
@@ -311,7 +311,7 @@ int launch(const CUtensorMap& mw, const CUtensorMap& ma, void* C, const SkinnyAr
               stream, mw, ma, (TOut*)C, a, status);
   int rc = hfee_check_launch("gemm_skinny");
   if (rc != HFEE_OK || a.splits == 1) return rc;
-  const long long outs = (long long)a.M * (EPI == EPI_SWIGLU ? a.N / 2 : a.N);
+  const long long outs = (long long)a.M * ((EPI == EPI_SWIGLU || EPI == EPI_GEGLU) ? a.N / 2 : a.N);
   hfee_launch(splitk_reduce_kernel<EPI, TOut>, dim3((unsigned)((outs + 255) / 256)), dim3(256), 0, stream,
               (const float*)a.workspace, (TOut*)C, a.ldc, a.M, a.N, a.splits);
   return hfee_check_launch("splitk_reduce");
@@ -323,6 +323,10 @@ int dispatch(const CUtensorMap& mw, const CUtensorMap& ma, void* C, int out_dtyp
   if (epilogue == EPI_ACCUM) {
     if (out_dtype != HFEE_F32) return hfee_fail(HFEE_ERR_ARG, "gemm_skinny: accumulate needs a float32 output");
     return launch<TN, EPI_ACCUM, float>(mw, ma, C, a, status, stream);
+  }
+  if (epilogue == EPI_GEGLU) {
+    if (out_dtype == HFEE_BF16) return launch<TN, EPI_GEGLU, __nv_bfloat16>(mw, ma, C, a, status, stream);
+    return launch<TN, EPI_GEGLU, float>(mw, ma, C, a, status, stream);
   }
   if (epilogue == EPI_SWIGLU) {
     if (out_dtype == HFEE_BF16) return launch<TN, EPI_SWIGLU, __nv_bfloat16>(mw, ma, C, a, status, stream);
@@ -353,9 +357,9 @@ HFEE_API int hfee_gemm_skinny(const void* A, long long lda, const void* W, long 
   HFEE_REQUIRE(lda % 8 == 0 && ldw % 8 == 0 && lda >= K && ldw >= K,
                "gemm_skinny: leading dimensions (%lld, %lld) must be multiples of 8 and at least K", lda, ldw);
   HFEE_REQUIRE(((uintptr_t)A % 16 == 0) && ((uintptr_t)W % 16 == 0), "gemm_skinny: operands must be 16-byte aligned");
-  HFEE_REQUIRE(epilogue >= 0 && epilogue <= 2, "gemm_skinny: unknown epilogue %d", epilogue);
-  HFEE_REQUIRE(epilogue != EPI_SWIGLU || N % 8 == 0, "gemm_skinny: SwiGLU needs N %% 8 == 0, got %d", N);
-  HFEE_REQUIRE(ldc >= (epilogue == EPI_SWIGLU ? N / 2 : N), "gemm_skinny: ldc=%lld is too small", ldc);
+  HFEE_REQUIRE((epilogue >= 0 && epilogue <= 2) || epilogue == EPI_GEGLU, "gemm_skinny: unknown epilogue %d", epilogue);
+  HFEE_REQUIRE((epilogue != EPI_SWIGLU && epilogue != EPI_GEGLU) || N % 8 == 0, "gemm_skinny: SwiGLU needs N %% 8 == 0, got %d", N);
+  HFEE_REQUIRE(ldc >= ((epilogue == EPI_SWIGLU || epilogue == EPI_GEGLU) ? N / 2 : N), "gemm_skinny: ldc=%lld is too small", ldc);
   SkinnyArgs a;
   a.M = M; a.N = N; a.K = K;
   a.w_tiles = (N + WM - 1) / WM;

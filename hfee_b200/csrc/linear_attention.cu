@@ -21,8 +21,10 @@
 // which is the recurrence written out.  Three passes so that the runs of a long prompt work in
 // parallel: (1) every run's own sum  sum_s decay^(n-1-s) k_s v_s^T, (2) per (request, head,
 // column tile) the states in front of every run, in order, and the request's new state, (3)
-// every run's outputs from the state in front of it.  All in float32 on the CUDA cores.
+// every run's outputs from the state in front of it.  In float32 on the CUDA cores for float32
+// activations and for sizes the tensor-core variant (further down) does not take.
 #include "common.cuh"
+#include "mma_tiles.cuh"
 
 namespace {
 
@@ -121,12 +123,13 @@ constexpr int LC_THREADS = 256;
 
 // The runs of all requests are numbered in batch order: request r's runs start at the sum over earlier
 // requests of ceil(count / LC_T).  A block finds (request, run within the request) for its number.
-__device__ __forceinline__ int runs_of(int count) { return (count + LC_T - 1) / LC_T; }
+template <int RUN> __device__ __forceinline__ int runs_of(int count) { return (count + RUN - 1) / RUN; }
 
+template <int RUN>
 __device__ __forceinline__ bool find_run(const int* __restrict__ cu_tokens, int requests, int number, int* req, int* run) {
   int base = 0;
   for (int r = 0; r < requests; ++r) {
-    const int c = runs_of(cu_tokens[r + 1] - cu_tokens[r]);
+    const int c = runs_of<RUN>(cu_tokens[r + 1] - cu_tokens[r]);
     if (number < base + c) { *req = r; *run = number - base; return true; }
     base += c;
   }
@@ -143,7 +146,7 @@ la_chunk_sums_kernel(const T* __restrict__ k, const T* __restrict__ v, long long
   const int head = blockIdx.x;
   const int c0 = blockIdx.z * LC_COLS;
   int req = 0, run = 0;
-  const bool mine = find_run(cu_tokens, requests, blockIdx.y, &req, &run);
+  const bool mine = find_run<LC_T>(cu_tokens, requests, blockIdx.y, &req, &run);
   pdl_wait();
   pdl_launch_dependents();
   if (!mine) return;
@@ -173,6 +176,7 @@ la_chunk_sums_kernel(const T* __restrict__ k, const T* __restrict__ v, long long
 
 // (2) in place: sums[run] becomes the state in front of run `run`; the request's state becomes the one
 // behind its last run.  One thread per state element walks the runs in order.
+template <int RUN>
 __global__ void la_chunk_scan_kernel(const float* __restrict__ decay, const int* __restrict__ cu_tokens,
                                      const int* __restrict__ slots, float* __restrict__ sums, float* __restrict__ state,
                                      int heads, int dim, int vdim, int write_state) {
@@ -180,22 +184,32 @@ __global__ void la_chunk_scan_kernel(const float* __restrict__ decay, const int*
   const int count = cu_tokens[req + 1] - cu_tokens[req];
   const int slot = slots[req];
   int first_run = 0;
-  for (int r = 0; r < req; ++r) first_run += runs_of(cu_tokens[r + 1] - cu_tokens[r]);
+  for (int r = 0; r < req; ++r) first_run += runs_of<RUN>(cu_tokens[r + 1] - cu_tokens[r]);
   pdl_wait();
   pdl_launch_dependents();
   if (count <= 0) return;
   const float lam = decay[head];
-  const int runs = runs_of(count);
+  const int runs = runs_of<RUN>(count);
+  const float lam_full = powf(lam, (float)RUN);
   const long long per = (long long)dim * vdim;
   float* S_g = state + ((long long)slot * heads + head) * per;
   for (long long e = (long long)blockIdx.z * blockDim.x + threadIdx.x; e < per; e += (long long)gridDim.z * blockDim.x) {
     float S = S_g[e];
-    for (int run = 0; run < runs; ++run) {
-      const int n = min(LC_T, count - run * LC_T);
-      float* A = sums + ((long long)(first_run + run) * heads + head) * per + e;
-      const float own = *A;
-      *A = S;
-      S = fmaf(powf(lam, (float)n), S, own);
+    float* A0 = sums + ((long long)first_run * heads + head) * per + e;
+    const long long stride = (long long)heads * per;
+    for (int base = 0; base < runs; base += 8) {          // eight runs' sums are requested before the first is used
+      float own[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) own[i] = base + i < runs ? A0[(base + i) * stride] : 0.f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int run = base + i;
+        if (run < runs) {
+          const int n = min(RUN, count - run * RUN);
+          A0[run * stride] = S;
+          S = fmaf(n == RUN ? lam_full : powf(lam, (float)n), S, own[i]);
+        }
+      }
     }
     if (write_state) S_g[e] = S;
   }
@@ -211,7 +225,7 @@ la_chunk_out_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* _
   const int head = blockIdx.x;
   const int c0 = blockIdx.z * LC_COLS;
   int req = 0, run = 0;
-  const bool mine = find_run(cu_tokens, requests, blockIdx.y, &req, &run);
+  const bool mine = find_run<LC_T>(cu_tokens, requests, blockIdx.y, &req, &run);
   pdl_wait();
   pdl_launch_dependents();
   if (!mine) return;
@@ -256,6 +270,266 @@ la_chunk_out_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* _
   }
 }
 
+
+// ------------------------------------------------------------------------------------------ chunked, tensor cores
+// The same three passes with runs of LM_T tokens and the products on mma.sync (bfloat16 in, float32 out).
+// q, k and v enter as the bfloat16 values of their activations.  Everything else that a product reads is a
+// float32 quantity and goes in as the sum of two bfloat16 numbers (the value rounded, and what the rounding
+// left), each with a product of its own: the decayed keys k_s decay^(n-1-s), the weights
+// decay^(t-s) (q_t . k_s), and the state in front of the run.  Sums are float32.
+constexpr int LM_T = 64;
+constexpr int LM_COLS = 64;
+constexpr int LM_WARPS = 4;
+constexpr int LM_PAD = 8;          // bfloat16 per shared-memory row beyond its content: fragment loads meet no bank twice
+struct alignas(16) Pack8 { bf16 v[8]; };
+
+// (1) sums[run number][head] = sum_s (k_s decay^(n-1-s)) v_s^T
+template <int ACT>
+__global__ void __launch_bounds__(LM_WARPS * 32)
+la_mma_sums_kernel(const bf16* __restrict__ k, const bf16* __restrict__ v, long long ld, const float* __restrict__ decay,
+                   const int* __restrict__ cu_tokens, float* __restrict__ sums, int requests, int heads, int dim, int vdim) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int head = blockIdx.x, c0 = blockIdx.z * LM_COLS;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  int req = 0, run = 0;
+  const bool mine = find_run<LM_T>(cu_tokens, requests, blockIdx.y, &req, &run);
+  pdl_wait();
+  pdl_launch_dependents();
+  if (!mine) return;
+  const int begin = cu_tokens[req], count = cu_tokens[req + 1] - begin;
+  const int t0 = run * LM_T, n = min(LM_T, count - t0);
+  const float lam = decay[head];
+  constexpr int LDT = LM_T + LM_PAD;
+  bf16* kt_hi = reinterpret_cast<bf16*>(smem_raw);       // [dim][LDT]  (k_s decay^(n-1-s)) transposed
+  bf16* kt_lo = kt_hi + dim * LDT;
+  bf16* vt = kt_lo + dim * LDT;                          // [LM_COLS][LDT]
+  float* pw = reinterpret_cast<float*>(vt + LM_COLS * LDT);   // decay^i, i = 0..LM_T
+  for (int i = threadIdx.x; i <= LM_T; i += LM_WARPS * 32) pw[i] = powf(lam, (float)i);
+  __syncthreads();
+  // 16-byte loads: a thread takes 8 consecutive dimensions of one token
+  const int dv = dim / 8;
+  for (int e = threadIdx.x; e < LM_T * dv; e += LM_WARPS * 32) {
+    const int s = e / dv, d = (e % dv) * 8;
+    Pack8 raw = {};
+    if (s < n) raw = *reinterpret_cast<const Pack8*>(k + (long long)(begin + t0 + s) * ld + (long long)head * dim + d);
+    const float w = s < n ? pw[n - 1 - s] : 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float kb = __bfloat162float(__float2bfloat16_rn(activate<ACT>(__bfloat162float(raw.v[i]))));
+      split_bf16(kb * w, &kt_hi[(d + i) * LDT + s], &kt_lo[(d + i) * LDT + s]);
+    }
+  }
+  for (int e = threadIdx.x; e < LM_T * (LM_COLS / 8); e += LM_WARPS * 32) {
+    const int s = e / (LM_COLS / 8), j = (e % (LM_COLS / 8)) * 8, c = c0 + j;
+    Pack8 raw = {};
+    if (s < n && c < vdim) raw = *reinterpret_cast<const Pack8*>(v + (long long)(begin + t0 + s) * ld + (long long)head * vdim + c);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) vt[(j + i) * LDT + s] = __float2bfloat16_rn(activate<ACT>(__bfloat162float(raw.v[i])));
+  }
+  __syncthreads();
+  float* A = sums + (((long long)blockIdx.y * heads + head) * dim) * vdim;
+  const int g = lane >> 2, t = lane & 3;
+  for (int d0 = warp * 16; d0 < dim; d0 += LM_WARPS * 16) {
+    float acc[LM_COLS / 8][4];
+#pragma unroll
+    for (int nt = 0; nt < LM_COLS / 8; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
+#pragma unroll
+    for (int ks = 0; ks < LM_T / 16; ++ks) {
+      uint32_t ah[4], al[4];
+      load_a(ah, kt_hi, LDT, d0, ks * 16, lane);
+      load_a(al, kt_lo, LDT, d0, ks * 16, lane);
+#pragma unroll
+      for (int nt = 0; nt < LM_COLS / 8; ++nt) {
+        uint32_t b0, b1;
+        load_b(b0, b1, vt, LDT, nt * 8, ks * 16, lane);
+        mma_bf16(acc[nt], ah, b0, b1);
+        mma_bf16(acc[nt], al, b0, b1);
+      }
+    }
+#pragma unroll
+    for (int nt = 0; nt < LM_COLS / 8; ++nt) {
+      const int c = c0 + nt * 8 + 2 * t;
+      float* r0 = A + (long long)(d0 + g) * vdim + c;
+      float* r1 = A + (long long)(d0 + g + 8) * vdim + c;
+      if (c < vdim) { r0[0] = acc[nt][0]; r1[0] = acc[nt][2]; }
+      if (c + 1 < vdim) { r0[1] = acc[nt][1]; r1[1] = acc[nt][3]; }
+    }
+  }
+}
+
+// (3) o_t = decay^(t+1) S_in^T q_t + sum_{s <= t} decay^(t-s) (q_t . k_s) v_s; warp w owns rows 16w..16w+15 of the run
+template <int ACT>
+__global__ void __launch_bounds__(LM_WARPS * 32)
+la_mma_out_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, const bf16* __restrict__ v, long long ld,
+                  const float* __restrict__ decay, const int* __restrict__ cu_tokens, const float* __restrict__ sums,
+                  float* __restrict__ out, long long ld_o, int requests, int heads, int dim, int vdim) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int head = blockIdx.x, c0 = blockIdx.z * LM_COLS;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  int req = 0, run = 0;
+  const bool mine = find_run<LM_T>(cu_tokens, requests, blockIdx.y, &req, &run);
+  pdl_wait();
+  pdl_launch_dependents();
+  if (!mine) return;
+  const int begin = cu_tokens[req], count = cu_tokens[req + 1] - begin;
+  const int t0 = run * LM_T, n = min(LM_T, count - t0);
+  const float lam = decay[head];
+  const int LDD = dim + LM_PAD;
+  constexpr int LDT = LM_T + LM_PAD;
+  bf16* qs = reinterpret_cast<bf16*>(smem_raw);          // [LM_T][LDD]
+  bf16* ks_ = qs + LM_T * LDD;                           // [LM_T][LDD]
+  bf16* st_hi = ks_ + LM_T * LDD;                        // [LM_COLS][LDD]  the state in front of the run, transposed
+  bf16* st_lo = st_hi + LM_COLS * LDD;
+  bf16* vt = st_lo + LM_COLS * LDD;                      // [LM_COLS][LDT]
+  bf16* p_hi = vt + LM_COLS * LDT;                       // [LM_T][LDT]
+  bf16* p_lo = p_hi + LM_T * LDT;
+  float* pw = reinterpret_cast<float*>(p_lo + LM_T * LDT);   // decay^i, i = 0..LM_T
+  // 16-byte loads: a thread takes 8 consecutive dimensions of one token (4 columns of one state row)
+  const int dv = dim / 8;
+  for (int e = threadIdx.x; e < LM_T * dv; e += LM_WARPS * 32) {
+    const int s = e / dv, d = (e % dv) * 8;
+    Pack8 rq = {}, rk = {};
+    if (s < n) {
+      const long long at = (long long)(begin + t0 + s) * ld + (long long)head * dim + d;
+      rq = *reinterpret_cast<const Pack8*>(q + at);
+      rk = *reinterpret_cast<const Pack8*>(k + at);
+    }
+    Pack8 oq, ok;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      oq.v[i] = __float2bfloat16_rn(activate<ACT>(__bfloat162float(rq.v[i])));
+      ok.v[i] = __float2bfloat16_rn(activate<ACT>(__bfloat162float(rk.v[i])));
+    }
+    *reinterpret_cast<Pack8*>(qs + s * LDD + d) = oq;
+    *reinterpret_cast<Pack8*>(ks_ + s * LDD + d) = ok;
+  }
+  for (int e = threadIdx.x; e < LM_T * (LM_COLS / 8); e += LM_WARPS * 32) {
+    const int s = e / (LM_COLS / 8), j = (e % (LM_COLS / 8)) * 8, c = c0 + j;
+    Pack8 raw = {};
+    if (s < n && c < vdim) raw = *reinterpret_cast<const Pack8*>(v + (long long)(begin + t0 + s) * ld + (long long)head * vdim + c);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) vt[(j + i) * LDT + s] = __float2bfloat16_rn(activate<ACT>(__bfloat162float(raw.v[i])));
+  }
+  const float* S_in = sums + (((long long)blockIdx.y * heads + head) * dim) * vdim;
+  for (int e = threadIdx.x; e < dim * (LM_COLS / 4); e += LM_WARPS * 32) {
+    const int d = e / (LM_COLS / 4), j = (e % (LM_COLS / 4)) * 4, c = c0 + j;
+    float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (c < vdim) x = *reinterpret_cast<const float4*>(S_in + (long long)d * vdim + c);
+    split_bf16(x.x, &st_hi[(j + 0) * LDD + d], &st_lo[(j + 0) * LDD + d]);
+    split_bf16(x.y, &st_hi[(j + 1) * LDD + d], &st_lo[(j + 1) * LDD + d]);
+    split_bf16(x.z, &st_hi[(j + 2) * LDD + d], &st_lo[(j + 2) * LDD + d]);
+    split_bf16(x.w, &st_hi[(j + 3) * LDD + d], &st_lo[(j + 3) * LDD + d]);
+  }
+  for (int i = threadIdx.x; i <= LM_T; i += LM_WARPS * 32) pw[i] = powf(lam, (float)i);
+  __syncthreads();
+
+  const int g = lane >> 2, t = lane & 3;
+  const int r0 = warp * 16;
+  if (r0 >= n) return;
+  float acc[LM_T / 8][4];
+  // weights of the warp's rows: keys in blocks of 8 up to the diagonal
+  const int key_tiles = r0 / 8 + 2;
+#pragma unroll
+  for (int nt = 0; nt < LM_T / 8; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
+  for (int kk = 0; kk < dim; kk += 16) {
+    uint32_t a[4];
+    load_a(a, qs, LDD, r0, kk, lane);
+#pragma unroll
+    for (int nt = 0; nt < LM_T / 8; ++nt) {
+      if (nt < key_tiles) {
+        uint32_t b0, b1;
+        load_b(b0, b1, ks_, LDD, nt * 8, kk, lane);
+        mma_bf16(acc[nt], a, b0, b1);
+      }
+    }
+  }
+#pragma unroll
+  for (int nt = 0; nt < LM_T / 8; ++nt) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int row = r0 + g + (i >= 2 ? 8 : 0), col = nt * 8 + 2 * t + (i & 1);
+      const float w = (nt < key_tiles && col <= row) ? acc[nt][i] * pw[row - col] : 0.f;
+      split_bf16(w, &p_hi[row * LDT + col], &p_lo[row * LDT + col]);
+    }
+  }
+  __syncwarp();
+  // the rows' outputs: intra-run part into acc, the part of the state in front of the run into acc_s
+  float acc_s[LM_COLS / 8][4];
+#pragma unroll
+  for (int nt = 0; nt < LM_COLS / 8; ++nt) {
+    acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
+    acc_s[nt][0] = acc_s[nt][1] = acc_s[nt][2] = acc_s[nt][3] = 0.f;
+  }
+  for (int ks = 0; ks <= warp; ++ks) {                  // key blocks of 16 up to the diagonal
+    uint32_t ah[4], al[4];
+    load_a(ah, p_hi, LDT, r0, ks * 16, lane);
+    load_a(al, p_lo, LDT, r0, ks * 16, lane);
+#pragma unroll
+    for (int nt = 0; nt < LM_COLS / 8; ++nt) {
+      uint32_t b0, b1;
+      load_b(b0, b1, vt, LDT, nt * 8, ks * 16, lane);
+      mma_bf16(acc[nt], ah, b0, b1);
+      mma_bf16(acc[nt], al, b0, b1);
+    }
+  }
+  for (int kk = 0; kk < dim; kk += 16) {
+    uint32_t a[4];
+    load_a(a, qs, LDD, r0, kk, lane);
+#pragma unroll
+    for (int nt = 0; nt < LM_COLS / 8; ++nt) {
+      uint32_t b0, b1;
+      load_b(b0, b1, st_hi, LDD, nt * 8, kk, lane);
+      mma_bf16(acc_s[nt], a, b0, b1);
+      load_b(b0, b1, st_lo, LDD, nt * 8, kk, lane);
+      mma_bf16(acc_s[nt], a, b0, b1);
+    }
+  }
+#pragma unroll
+  for (int nt = 0; nt < LM_COLS / 8; ++nt) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int row = r0 + g + (i >= 2 ? 8 : 0), c = c0 + nt * 8 + 2 * t + (i & 1);
+      if (row < n && c < vdim)
+        out[(long long)(begin + t0 + row) * ld_o + (long long)head * vdim + c] = fmaf(pw[row + 1], acc_s[nt][i], acc[nt][i]);
+    }
+  }
+}
+
+size_t la_mma_out_smem(int dim) {
+  return sizeof(bf16) * ((size_t)2 * LM_T * (dim + LM_PAD) + 2 * LM_COLS * (dim + LM_PAD) + LM_COLS * (LM_T + LM_PAD) +
+                         2 * LM_T * (LM_T + LM_PAD)) + sizeof(float) * (LM_T + 1);
+}
+
+// key sizes in steps of 16, value sizes in steps of 8 and rows that 16-byte loads can read
+bool la_mma_takes(int dim, int vdim, long long ld, const void* q, const void* k, const void* v) {
+  return dim % 16 == 0 && vdim % 8 == 0 && dim <= LA_MAX_DIM && ld % 8 == 0 && la_mma_out_smem(dim) <= 200 * 1024 &&
+         (uintptr_t)q % 16 == 0 && (uintptr_t)k % 16 == 0 && (uintptr_t)v % 16 == 0;
+}
+
+int launch_chunked_mma(const void* q, const void* k, const void* v, long long ld, const float* decay, float* state,
+                       const int* cu_tokens, const int* slots, float* out, long long ld_o, float* sums, int requests,
+                       int tokens, int heads, int dim, int vdim, int activation, int write_state, cudaStream_t stream) {
+  const unsigned tiles = (unsigned)((vdim + LM_COLS - 1) / LM_COLS);
+  const dim3 grid(heads, (unsigned)(tokens / LM_T + requests), tiles);
+  const size_t smem1 = sizeof(bf16) * ((size_t)2 * dim * (LM_T + LM_PAD) + LM_COLS * (LM_T + LM_PAD)) + sizeof(float) * (LM_T + 1);
+  const size_t smem3 = la_mma_out_smem(dim);
+  auto go = [&](auto sums_kernel, auto out_kernel) {
+    if (smem1 > 48 * 1024) cudaFuncSetAttribute(sums_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem1);
+    if (smem3 > 48 * 1024) cudaFuncSetAttribute(out_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem3);
+    hfee_launch(sums_kernel, grid, dim3(LM_WARPS * 32), smem1, stream, (const bf16*)k, (const bf16*)v, ld, decay, cu_tokens,
+                sums, requests, heads, dim, vdim);
+    const long long per = (long long)dim * vdim;
+    const unsigned z = (unsigned)((per + 255) / 256 < 64 ? (per + 255) / 256 : 64);
+    hfee_launch(la_chunk_scan_kernel<LM_T>, dim3(heads, requests, z), dim3(256), 0, stream, decay, cu_tokens, slots, sums,
+                state, heads, dim, vdim, write_state);
+    hfee_launch(out_kernel, grid, dim3(LM_WARPS * 32), smem3, stream, (const bf16*)q, (const bf16*)k, (const bf16*)v, ld,
+                decay, cu_tokens, (const float*)sums, out, ld_o, requests, heads, dim, vdim);
+  };
+  if (activation == ACT_SILU) go(la_mma_sums_kernel<ACT_SILU>, la_mma_out_kernel<ACT_SILU>);
+  else go(la_mma_sums_kernel<ACT_NONE>, la_mma_out_kernel<ACT_NONE>);
+  return hfee_check_launch("linear_attention_chunked (tensor cores)");
+}
+
 template <typename T>
 int launch_recurrent(const void* q, const void* k, const void* v, long long ld, const float* decay, float* state,
                      const int* cu_tokens, const int* slots, float* out, long long ld_o, int requests, int heads, int dim,
@@ -288,7 +562,7 @@ int launch_chunked(const void* q, const void* k, const void* v, long long ld, co
                 requests, heads, dim, vdim);
     const long long per = (long long)dim * vdim;
     const unsigned z = (unsigned)((per + 255) / 256 < 64 ? (per + 255) / 256 : 64);
-    hfee_launch(la_chunk_scan_kernel, dim3(heads, requests, z), dim3(256), 0, stream, decay, cu_tokens, slots, sums, state,
+    hfee_launch(la_chunk_scan_kernel<LC_T>, dim3(heads, requests, z), dim3(256), 0, stream, decay, cu_tokens, slots, sums, state,
                 heads, dim, vdim, write_state);
     hfee_launch(out_kernel, grid, dim3(LC_THREADS), smem3, stream, (const T*)q, (const T*)k, (const T*)v, ld, decay,
                 cu_tokens, (const float*)sums, out, ld_o, requests, heads, dim, vdim);
@@ -331,13 +605,15 @@ HFEE_API int hfee_linear_attention_chunked(const void* q, const void* k, const v
                                            const float* decay, float* state, const int* cu_tokens, const int* slots,
                                            float* out, long long ld_o, float* workspace, long long workspace_floats,
                                            int requests, int tokens, int heads, int dim, int vdim, int activation,
-                                           int write_state, cudaStream_t stream) {
+                                           int write_state, int tensor_cores, cudaStream_t stream) {
   if (requests == 0 || tokens == 0) return HFEE_OK;
   if (int e = check_sizes("linear_attention_chunked", requests, heads, dim, vdim, ld, ld_o, activation)) return e;
   HFEE_REQUIRE(workspace != nullptr && workspace_floats >= hfee_linear_attention_chunked_workspace(requests, tokens, heads, dim, vdim),
                "linear_attention_chunked: the workspace is too small");
   if (dtype == HFEE_F32)
     return launch_chunked<float>(q, k, v, ld, decay, state, cu_tokens, slots, out, ld_o, workspace, requests, tokens, heads, dim, vdim, activation, write_state, stream);
+  if (dtype == HFEE_BF16 && tensor_cores && la_mma_takes(dim, vdim, ld, q, k, v))
+    return launch_chunked_mma(q, k, v, ld, decay, state, cu_tokens, slots, out, ld_o, workspace, requests, tokens, heads, dim, vdim, activation, write_state, stream);
   if (dtype == HFEE_BF16)
     return launch_chunked<__nv_bfloat16>(q, k, v, ld, decay, state, cu_tokens, slots, out, ld_o, workspace, requests, tokens, heads, dim, vdim, activation, write_state, stream);
   return hfee_fail(HFEE_ERR_ARG, "linear_attention_chunked: unknown dtype %d", dtype);

@@ -52,8 +52,14 @@ short_conv_kernel(const float* __restrict__ x, const float* __restrict__ w, floa
     }
   }
   if (mode & SC_OUT) {
-    for (int t = first; t < last; ++t) {
-      const float xv = xc[(long long)t * width];
+    float xin[SC_TOKENS];                     // the run's inputs, requested together
+#pragma unroll
+    for (int i = 0; i < SC_TOKENS; ++i) xin[i] = first + i < last ? xc[(long long)(first + i) * width] : 0.f;
+#pragma unroll
+    for (int i = 0; i < SC_TOKENS; ++i) {
+      const int t = first + i;
+      if (t >= last) break;
+      const float xv = xin[i];
       float acc = 0.f;
 #pragma unroll
       for (int j = 0; j < SC_MAX_TAPS; ++j) {

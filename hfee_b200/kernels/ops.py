@@ -49,11 +49,13 @@ _SIGNATURES = {
     "hfee_gemm_simt": [_P, _L, _P, _L, _I, _P, _L, _I, _I, _I, _I, _I, _P],
     "hfee_attention_simt": [_P, _I, _P, _P, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _P],
     "hfee_attention_simt_masked": [_P, _I, _P, _P, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _P, _P, _P, _L, _I, _P],
+    "hfee_attention_sigmoid_mma": [_P, _L, _P, _P, _P, _I, _I, _P, _P, _P, _P, _L, _I, _I, _I, _I, _I, _F, _I, _I, _P, _P, _P, _L, _P],
+    "hfee_attention_sigmoid_mma_supports": [_I, _I, _I],
     "hfee_short_conv": [_P, _P, _P, _P, _P, _P, _L, _I, _I, _I, _I, _I, _I, _P],
     "hfee_short_conv_launches": [_I, _I, _I],
     "hfee_linear_attention": [_P, _P, _P, _L, _I, _P, _P, _P, _P, _P, _L, _I, _I, _I, _I, _I, _I, _P],
-    "hfee_linear_attention_chunked": [_P, _P, _P, _L, _I, _P, _P, _P, _P, _P, _L, _P, _L, _I, _I, _I, _I, _I, _I, _I, _P],
-    "hfee_rmsnorm_add": [_P, _L, _P, _P, _I, _I, _F, _I, _P],
+    "hfee_linear_attention_chunked": [_P, _P, _P, _L, _I, _P, _P, _P, _P, _P, _L, _P, _L, _I, _I, _I, _I, _I, _I, _I, _I, _P],
+    "hfee_rmsnorm_add": [_P, _L, _P, _P, _I, _I, _F, _I, _P, _L, _I, _P],
     "hfee_norm_gate": [_P, _L, _P, _F, _P, _L, _P, _L, _I, _I, _I, _P],
     "hfee_gated_act": [_P, _L, _P, _L, _I, _I, _I, _I, _I, _P],
     "hfee_scale_f32": [_P, _L, _I, _I, _F, _P],
@@ -349,7 +351,8 @@ def gemm_simt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: b
 
 STREAM_MAX_TOKENS = 64
 USE_TCGEN05 = True
-EPI_STORE, EPI_ACCUM, EPI_SWIGLU = 0, 1, 2
+EPI_STORE, EPI_ACCUM, EPI_SWIGLU, EPI_GEGLU = 0, 1, 2, 4
+EPI_GATED = (EPI_SWIGLU, EPI_GEGLU)         # out = act(gate) * up over rows of w interleaved as [4 gate | 4 up]
 
 
 def _streamable(a: torch.Tensor, w: torch.Tensor) -> bool:
@@ -366,7 +369,7 @@ def gemm_stream(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: i
     m, k = a.shape
     n = w.shape[0]
     assert w.shape[1] == k and a.dtype == w.dtype == torch.bfloat16
-    assert tuple(out.shape) == (m, n // 2 if epilogue == EPI_SWIGLU else n)
+    assert tuple(out.shape) == (m, n // 2 if epilogue in EPI_GATED else n)
     _check(lib.hfee_gemm_stream(a.data_ptr(), _rows(a, "gemm a"), w.data_ptr(), _rows(w, "gemm w"), out.data_ptr(),
                                 _rows(out, "gemm out"), _dt(out), epilogue, m, n, k, _stream()), lib)
 
@@ -381,7 +384,7 @@ def gemm_ring(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int
     m, k = a.shape
     n = w.shape[0]
     assert w.shape[1] == k and a.dtype == w.dtype == torch.bfloat16
-    assert tuple(out.shape) == (m, n // 2 if epilogue == EPI_SWIGLU else n)
+    assert tuple(out.shape) == (m, n // 2 if epilogue in EPI_GATED else n)
     _check(lib.hfee_gemm_ring(a.data_ptr(), _rows(a, "gemm a"), w.data_ptr(), _rows(w, "gemm w"), out.data_ptr(),
                               _rows(out, "gemm out"), _dt(out), epilogue, m, n, k, _status().data_ptr(), _stream()), lib)
 
@@ -423,7 +426,7 @@ def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: 
     m, k = a.shape
     n = w.shape[0]
     assert w.shape[1] == k and a.dtype == w.dtype == torch.bfloat16
-    assert tuple(out.shape) == (m, n // 2 if epilogue == EPI_SWIGLU else n)
+    assert tuple(out.shape) == (m, n // 2 if epilogue in EPI_GATED else n)
     tiles_256 = 0
     if block_n is None:
         # wide tiles need a third less shared-memory feed per flop (a 128-wide tile's feed rate is at
@@ -463,7 +466,7 @@ def gemm_tcgen05_pair(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilo
     m, k = a.shape
     n = w.shape[0]
     assert w.shape[1] == k and a.dtype == w.dtype == torch.bfloat16
-    assert tuple(out.shape) == (m, n // 2 if epilogue == EPI_SWIGLU else n)
+    assert tuple(out.shape) == (m, n // 2 if epilogue in EPI_GATED else n)
     _check(lib.hfee_gemm_tcgen05_pair(a.data_ptr(), _rows(a, "gemm a"), w.data_ptr(), _rows(w, "gemm w"), out.data_ptr(),
                                       _rows(out, "gemm out"), _dt(out), epilogue, m, n, k, _status().data_ptr(),
                                       _stream()), lib)
@@ -495,7 +498,7 @@ def gemm_stream_norm(x: torch.Tensor, norm_weight: torch.Tensor, eps: float, w: 
     n = w.shape[0]
     assert x.dtype == torch.float32 and norm_weight.dtype == torch.float32 and norm_weight.numel() == k
     assert w.shape[1] == k and w.dtype == torch.bfloat16
-    assert tuple(out.shape) == (m, n // 2 if epilogue == EPI_SWIGLU else n)
+    assert tuple(out.shape) == (m, n // 2 if epilogue in EPI_GATED else n)
     _check(lib.hfee_gemm_stream_norm(x.data_ptr(), _rows(x, "x"), _ptr(rows), norm_weight.data_ptr(), float(eps),
                                      int(add_unit), w.data_ptr(), _rows(w, "gemm w"), out.data_ptr(),
                                      _rows(out, "gemm out"), _dt(out), epilogue, m, n, k, _stream()), lib)
@@ -564,7 +567,7 @@ def gemm_skinny(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: i
     m, k = a.shape
     n = w.shape[0]
     assert w.shape[1] == k and a.dtype == w.dtype == torch.bfloat16
-    assert tuple(out.shape) == (m, n // 2 if epilogue == EPI_SWIGLU else n)
+    assert tuple(out.shape) == (m, n // 2 if epilogue in EPI_GATED else n)
     ws = _skinny_workspace()
     _check(lib.hfee_gemm_skinny(a.data_ptr(), _rows(a, "gemm a"), w.data_ptr(), _rows(w, "gemm w"), out.data_ptr(),
                                 _rows(out, "gemm out"), _dt(out), epilogue, m, n, k, ws.data_ptr(), ws.numel(),
@@ -589,7 +592,7 @@ def _small_gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: i
     elif m <= STREAM_BEST_TOKENS or not USE_TCGEN05:
         gemm_stream(a, w, out, epilogue)
     elif m > 32 and 64 * 128 <= n <= 256 * 128 and a.shape[1] <= 4096 and _tensor_core_ok(a, w) and (
-            epilogue != EPI_SWIGLU or out.dtype == torch.bfloat16):
+            epilogue not in EPI_GATED or out.dtype == torch.bfloat16):
         # 64-256 narrow tiles of the large-tile kernel fill the SMs about once, and their epilogues are cheaper than the
         # swapped one: measured at 64 tokens, N = 16,384, K = 2,048: 16.3 us against 18.9 us
         gemm_tcgen05(a, w, out, epilogue)
@@ -616,27 +619,27 @@ SWIGLU_GRANULE = 4
 
 
 def linear_swiglu(a: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor, granule: int,
-                  scratch: torch.Tensor) -> None:
-    """out = silu(a @ w_gate^T) * (a @ w_up^T) where ``w_gate_up`` holds the rows of both in groups
+                  scratch: torch.Tensor, activation: str = "silu") -> None:
+    """out = act(a @ w_gate^T) * (a @ w_up^T) (``activation``: ``"silu"`` or ``"gelu_tanh"``) where ``w_gate_up`` holds the rows of both in groups
     of ``granule`` gate rows followed by ``granule`` up rows; ``scratch`` [m, 2*inner] holds the
     projection when it is not fused."""
     fusable = granule == SWIGLU_GRANULE and w_gate_up.shape[0] % 8 == 0
+    epilogue = EPI_SWIGLU if activation == "silu" else EPI_GEGLU
     if fusable and _streamable(a, w_gate_up):
-        _small_gemm(a, w_gate_up, out, EPI_SWIGLU)
+        _small_gemm(a, w_gate_up, out, epilogue)
     elif fusable and USE_TCGEN05 and _tensor_core_ok(a, w_gate_up) and out.dtype == torch.bfloat16:
-        gemm_tcgen05(a, w_gate_up, out, EPI_SWIGLU)
+        gemm_tcgen05(a, w_gate_up, out, epilogue)
     else:
         linear(a, w_gate_up, scratch)
-        swiglu(scratch, out, granule)
+        gated_act(scratch, out, activation, granule)
 
 
 def linear_gated_normed(inp, w_gate_up: torch.Tensor, out: torch.Tensor, granule: int, scratch: torch.Tensor,
                         activation: str) -> None:
-    """out = act(a @ w_gate^T) * (a @ w_up^T) for an activation other than SiLU: the projection goes to
-    ``scratch`` [m, 2*inner] and :func:`gated_act` applies the gate."""
+    """:func:`linear_swiglu` with another gate activation (``"gelu_tanh"``): in the product's epilogue where a
+    kernel with gated epilogues takes the shape, else through ``scratch`` [m, 2*inner] and :func:`gated_act`."""
     a = inp if isinstance(inp, torch.Tensor) else inp.tensor()
-    linear(a, w_gate_up, scratch)
-    gated_act(scratch, out, activation, granule)
+    linear_swiglu(a, w_gate_up, out, granule, scratch, activation)
 
 
 def attention_simt(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, block_table: torch.Tensor,
@@ -856,12 +859,14 @@ LINEAR_ATTENTION_CHUNKED_MIN = 8
 def linear_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay: torch.Tensor, state: torch.Tensor,
                      step, out: torch.Tensor, heads: int, dim: int, vdim: int, activation: str = "none",
                      write_state: bool = True, workspace: Optional[torch.Tensor] = None,
-                     chunked: Optional[bool] = None) -> None:
+                     chunked: Optional[bool] = None, tensor_cores: bool = True) -> None:
     """Linear attention with a decay per head over the step's tokens, continuing each request's float32 state
     ``state`` [slots, heads, dim, vdim]: S <- decay_h S + k v^T, o = S^T q.  ``q``, ``k``, ``v`` are column
     slices of one projection buffer (same row stride); ``activation`` is applied to them on the way in;
     ``out`` is float32 [n, heads * vdim].  Steps with a portion of several tokens take the chunked kernels
-    when ``workspace`` (float32, see :func:`linear_attention_workspace`) is given, else the token-by-token one."""
+    when ``workspace`` (float32, see :func:`linear_attention_workspace`) is given, else the token-by-token one;
+    the chunked kernels run on the tensor cores for bfloat16 activations and key sizes that are multiples of 16
+    (``tensor_cores=False``: on the CUDA cores)."""
     lib = library()
     n = q.shape[0]
     assert q.dtype == k.dtype == v.dtype and q.stride(0) == k.stride(0) == v.stride(0) and q.stride(1) == 1
@@ -878,7 +883,7 @@ def linear_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay: t
                                                  decay.data_ptr(), state.data_ptr(), step.cu_tokens.data_ptr(),
                                                  step.slots.data_ptr(), out.data_ptr(), _rows(out, "out"),
                                                  workspace.data_ptr(), workspace.numel(), step.r, step.n, heads,
-                                                 dim, vdim, act, int(write_state), _stream()), lib)
+                                                 dim, vdim, act, int(write_state), int(tensor_cores), _stream()), lib)
         count_launches(2)
         return
     _check(lib.hfee_linear_attention(q.data_ptr(), k.data_ptr(), v.data_ptr(), q.stride(0), _dt(q), decay.data_ptr(),
@@ -891,21 +896,56 @@ def linear_attention_workspace(requests: int, tokens: int, heads: int, dim: int,
     return int(library().hfee_linear_attention_chunked_workspace(requests, tokens, heads, dim, vdim))
 
 
+USE_SIGMOID_MMA = True
+_SIGMOID_MMA_TAKES: dict = {}
+
+
+def sigmoid_mma_supports(heads: int, kv_heads: int, head_dim: int) -> bool:
+    key = (heads, kv_heads, head_dim)
+    if key not in _SIGMOID_MMA_TAKES:
+        _SIGMOID_MMA_TAKES[key] = bool(library().hfee_attention_sigmoid_mma_supports(*key))
+    return _SIGMOID_MMA_TAKES[key]
+
+
 def sigmoid_attention(q, k_pool, v_pool, block_table, page_size, step, out, heads, kv_heads, head_dim, scale, window=0,
                       chunk=0, head_scale=None, head_bias=None, gate=None) -> None:
-    """Attention with unnormalised sigmoid weights over the cache, choosing the kernel for the dtype and the batch."""
+    """Attention with unnormalised sigmoid weights over the cache, choosing the kernel for the dtype and the
+    sizes: bfloat16 with a head size and a group the tensor-core kernel is built for runs there (prompt portions
+    and decode steps alike), everything else on the CUDA cores in float32."""
+    if USE_SIGMOID_MMA and q.dtype == torch.bfloat16 and sigmoid_mma_supports(heads, kv_heads, head_dim) and (
+            _rows(q, "q") % 2 == 0 and _rows(out, "out") % 2 == 0 and (gate is None or (_rows(gate, "gate") % 2 == 0
+                                                                                     and gate.data_ptr() % 4 == 0))):
+        lib = library()
+        for t, what in ((block_table, "block_table"), (step.cu_tokens, "cu_tokens"), (step.slots, "slots"),
+                        (step.context_before, "context_before")):
+            _i32(t, what)
+        assert k_pool.dtype == v_pool.dtype == out.dtype == torch.bfloat16 and k_pool.is_contiguous() and v_pool.is_contiguous()
+        assert tuple(k_pool.shape[1:]) == (kv_heads, page_size, head_dim) and q.shape == out.shape == (step.n, heads * head_dim)
+        _check(lib.hfee_attention_sigmoid_mma(q.data_ptr(), _rows(q, "q"), k_pool.data_ptr(), v_pool.data_ptr(),
+                                              block_table.data_ptr(), block_table.shape[1], page_size,
+                                              step.cu_tokens.data_ptr(), step.slots.data_ptr(), step.context_before.data_ptr(),
+                                              out.data_ptr(), _rows(out, "out"), step.n, step.r, heads, kv_heads, head_dim,
+                                              float(scale), int(window or 0), int(chunk or 0), _ptr(head_scale),
+                                              _ptr(head_bias), _ptr(gate), _rows(gate, "gate") if gate is not None else 0,
+                                              _stream()), lib)
+        return
     attention_simt_masked(q, k_pool, v_pool, block_table, page_size, step.positions, step.slot_of_token, out, heads,
                           kv_heads, head_dim, scale, window, chunk, WEIGHTS_SIGMOID, head_scale, head_bias, gate)
 
 
-def rmsnorm_add(y: torch.Tensor, weight: torch.Tensor, residual: torch.Tensor, eps: float, add_unit: bool = False) -> None:
-    """residual += y * rsqrt(mean(y^2) + eps) * weight, all float32."""
+def rmsnorm_add(y: torch.Tensor, weight: torch.Tensor, residual: torch.Tensor, eps: float, add_unit: bool = False,
+                cast_out: Optional[torch.Tensor] = None) -> None:
+    """residual += y * rsqrt(mean(y^2) + eps) * weight, all float32.  With ``cast_out`` the new residual rows
+    are also written there in its dtype (what the next matrix product reads)."""
     lib = library()
     assert y.dtype == residual.dtype == weight.dtype == torch.float32 and residual.is_contiguous()
     n, width = residual.shape
     assert y.shape == residual.shape and weight.numel() == width
+    assert cast_out is None or cast_out.shape == residual.shape
     _check(lib.hfee_rmsnorm_add(y.data_ptr(), _rows(y, "y"), weight.data_ptr(), residual.data_ptr(), n, width,
-                                float(eps), int(add_unit), _stream()), lib)
+                                float(eps), int(add_unit), _ptr(cast_out),
+                                _rows(cast_out, "cast_out") if cast_out is not None else 0,
+                                _dt(cast_out) if cast_out is not None else 0, _stream()), lib)
 
 
 def norm_gate(x: torch.Tensor, weight: Optional[torch.Tensor], eps: float, gate: torch.Tensor, out: torch.Tensor) -> None:
@@ -1050,7 +1090,7 @@ def argmax(logits: torch.Tensor, out: torch.Tensor, scratch: torch.Tensor, slots
 
 
 # the entry points the parts and the sampler launch through can be left out by class (see tag())
-for _name in ("attention_simt_masked", "short_conv", "linear_attention", "rmsnorm_add", "norm_gate", "gated_act", "scale_", "cast_rows",
+for _name in ("attention_simt_masked", "short_conv", "linear_attention", "rmsnorm_add", "norm_gate", "gated_act", "scale_", "cast_rows", "sigmoid_attention",
               "qk_norm_rope_cache", "embed", "rmsnorm", "rope_table", "rope_cache_write", "swiglu", "linear", "linear_normed", "linear_swiglu", "linear_rope_cache",
               "linear_swiglu_normed", "paged_attention", "paged_attention_rope", "sample", "argmax", "sample_chain"):
     globals()[_name] = _measurable(globals()[_name])

@@ -75,10 +75,17 @@ class OutputNormBlock(Block):
         else:
             h = self._as_input(residual, n)
         self._run(self.mixer, y, h, step, cache, writes_cache)
-        self.mixer_norm.forward_add(y, residual)
-        if self.feed_forward is not None:
-            self._run(self.feed_forward, y, self._as_input(residual, n), step)
-            self.ffn_norm.forward_add(y, residual)
+        if self.feed_forward is None:
+            self.mixer_norm.forward_add(y, residual)
+            return
+        if rt.dtype == torch.float32:
+            self.mixer_norm.forward_add(y, residual)
+            x = residual
+        else:       # the norm kernel also leaves the new residual in the feed-forward's input dtype
+            x = rt.scratch("block_normed", (rt.max_tokens, self.width))[:n]
+            self.mixer_norm.forward_add(y, residual, cast_out=x)
+        self._run(self.feed_forward, y, x, step)
+        self.ffn_norm.forward_add(y, residual)
 
     def _as_input(self, residual: torch.Tensor, n: int) -> torch.Tensor:
         """The residual stream in the dtype the matrix products read."""

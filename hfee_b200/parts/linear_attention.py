@@ -69,7 +69,7 @@ class DecayLinearAttention(Mixer):
         a, b = self.qk_cols, 2 * self.qk_cols
         q, k, v, g = proj[:, :a], proj[:, a:b], proj[:, b:b + self.vg_cols], proj[:, b + self.vg_cols:]
         o = rt.scratch("linattn_out", (rt.max_tokens, self.vg_cols), torch.float32)[:n]
-        ops.tag("attention")
+        ops.tag("linear_attention")
         workspace = None
         if step.max_new >= ops.LINEAR_ATTENTION_CHUNKED_MIN:
             # one state-sized sum per run of tokens; sized once for the engine's limits

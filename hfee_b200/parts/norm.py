@@ -34,10 +34,11 @@ class RMSNorm(Part):
         ops.tag(before)
 
 
-    def forward_add(self, y: torch.Tensor, residual: torch.Tensor) -> None:
-        """``residual += norm(y)``: the norm on a sublayer's output (both float32)."""
+    def forward_add(self, y: torch.Tensor, residual: torch.Tensor, cast_out: Optional[torch.Tensor] = None) -> None:
+        """``residual += norm(y)``: the norm on a sublayer's output (both float32); ``cast_out`` also takes
+        the new residual in the dtype the next matrix product reads."""
         before = ops.tag("norm")
-        ops.rmsnorm_add(y, self.weight, residual, self.eps, add_unit=self.add_unit)
+        ops.rmsnorm_add(y, self.weight, residual, self.eps, add_unit=self.add_unit, cast_out=cast_out)
         ops.tag(before)
 
     def fused_params(self):

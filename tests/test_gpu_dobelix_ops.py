@@ -65,7 +65,7 @@ def plain_linear_attention(q, k, v, decay, S):
 
 @pytest.mark.parametrize("heads,dim,vdim", [(2, 16, 16), (3, 40, 72), (1, 144, 24), (2, 64, 128)])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("chunked", [False, True])
+@pytest.mark.parametrize("chunked", [False, True, "cuda_cores"])
 def test_linear_attention_kernels(heads, dim, vdim, dtype, chunked):
     """Both kernels against the recurrence, over several steps that continue the state; slots out of order."""
     from hfee_b200.kernels import ops
@@ -86,12 +86,16 @@ def test_linear_attention_kernels(heads, dim, vdim, dtype, chunked):
         step = make_step([sizes[i] for i in live], slots=[slots[i] for i in live])
         q, k, v = x[:, :heads * dim], x[:, heads * dim:2 * heads * dim], x[:, 2 * heads * dim:]
         out = torch.empty((x.shape[0], heads * vdim), dtype=torch.float32, device=DEV)
-        ops.linear_attention(q, k, v, decay_d, state, step, out, heads, dim, vdim, "silu", True, ws, chunked=chunked)
+        ops.linear_attention(q, k, v, decay_d, state, step, out, heads, dim, vdim, "silu", True, ws, chunked=bool(chunked),
+                             tensor_cores=chunked is True)
         o = out.cpu().numpy()
         row = 0
         for i in live:
             n = sizes[i]
             xs = plain.silu(proj[i][at[i]:at[i] + n].double().cpu().numpy())
+            if chunked is True and dtype == torch.bfloat16 and dim % 16 == 0:
+                # the tensor-core kernels take q, k and v as the bfloat16 values of their activations
+                xs = torch.tensor(xs).to(torch.bfloat16).double().numpy()
             want, ref_state[i] = plain_linear_attention(xs[:, :heads * dim].reshape(n, heads, dim),
                                                         xs[:, heads * dim:2 * heads * dim].reshape(n, heads, dim),
                                                         xs[:, 2 * heads * dim:].reshape(n, heads, vdim), decay, ref_state[i])
@@ -114,6 +118,15 @@ def test_row_kernels(dtype):
     res_d = torch.tensor(res, dtype=torch.float32, device=DEV)
     ops.rmsnorm_add(torch.tensor(y, dtype=torch.float32, device=DEV), torch.tensor(w, dtype=torch.float32, device=DEV), res_d, 1e-3)
     assert np.max(np.abs(res_d.cpu().numpy() - (res + plain.rms_norm(y, w, 1e-3)))) < 1e-5
+
+    for wide in (136, 2048, 4102, 6144, 9000):        # the 16-byte variants (2 and 8 pieces a thread) and the plain kernel
+        yw, ww, rw = rng.normal(size=(5, wide)), 1 + rng.normal(size=wide) * 0.3, rng.normal(size=(5, wide))
+        r_d = torch.tensor(rw, dtype=torch.float32, device=DEV)
+        cast = torch.empty((5, wide), dtype=dtype, device=DEV)
+        ops.rmsnorm_add(torch.tensor(yw, dtype=torch.float32, device=DEV), torch.tensor(ww, dtype=torch.float32, device=DEV),
+                        r_d, 1e-3, cast_out=cast)
+        assert np.max(np.abs(r_d.cpu().numpy() - (rw + plain.rms_norm(yw, ww, 1e-3)))) < 2e-5
+        assert torch.equal(cast, r_d.to(dtype))
 
     g = torch.tensor(rng.normal(size=(n, width)), dtype=dtype, device=DEV)
     out = torch.empty((n, width), dtype=dtype, device=DEV)
@@ -142,8 +155,10 @@ def test_row_kernels(dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("heads,kv_heads,hd,rope_dim,chunk", [(4, 2, 16, 8, 5), (3, 1, 40, 40, 16), (2, 2, 24, 0, 0)])
-def test_qk_norm_rope_and_sigmoid_attention(dtype, heads, kv_heads, hd, rope_dim, chunk):
+@pytest.mark.parametrize("heads,kv_heads,hd,rope_dim,chunk", [(4, 2, 16, 8, 5), (3, 1, 40, 40, 16), (2, 2, 24, 0, 0),
+                                                              (8, 2, 32, 32, 13), (4, 4, 64, 16, 70), (16, 1, 48, 48, 9)])
+@pytest.mark.parametrize("kernel", ["cuda_cores", "chosen"])
+def test_qk_norm_rope_and_sigmoid_attention(dtype, heads, kv_heads, hd, rope_dim, chunk, kernel):
     """Norm over the whole projection, rotation of the leading dimensions, values = keys as projected, pages in
     scrambled order, sigmoid weights inside chunks, output gate; two requests, the second continuing its cache."""
     from hfee_b200.kernels import ops
@@ -177,8 +192,12 @@ def test_qk_norm_rope_and_sigmoid_attention(dtype, heads, kv_heads, hd, rope_dim
         ops.qk_norm_rope_cache(x, f32(wq), f32(wk), eps, cs, rope_dim, step.positions, step.slot_of_token, q, k_pool, v_pool,
                                table, page, heads, kv_heads, hd)
         out = torch.empty_like(q)
-        ops.attention_simt_masked(q, k_pool, v_pool, table, page, step.positions, step.slot_of_token, out, heads, kv_heads,
-                                  hd, scale, 0, chunk, ops.WEIGHTS_SIGMOID, f32(temp), f32(bias), g)
+        if kernel == "chosen":       # the tensor-core kernel where it takes the sizes
+            ops.sigmoid_attention(q, k_pool, v_pool, table, page, step, out, heads, kv_heads, hd, scale, 0, chunk,
+                                  f32(temp), f32(bias), g)
+        else:
+            ops.attention_simt_masked(q, k_pool, v_pool, table, page, step.positions, step.slot_of_token, out, heads,
+                                      kv_heads, hd, scale, 0, chunk, ops.WEIGHTS_SIGMOID, f32(temp), f32(bias), g)
         o = out.double().cpu().numpy()
         at = 0
         for i in live:
@@ -201,3 +220,26 @@ def test_qk_norm_rope_and_sigmoid_attention(dtype, heads, kv_heads, hd, rope_dim
         want = want.reshape(n, -1) * plain.sigmoid(gates[i].double().cpu().numpy())
         tol = 2e-5 if dtype == torch.float32 else 3e-2
         assert np.max(np.abs(np.concatenate(got[i]) - want)) < tol * np.max(np.abs(want))
+
+
+@pytest.mark.parametrize("m", [1, 7, 16, 40, 300])
+@pytest.mark.parametrize("activation", ["gelu_tanh", "silu"])
+def test_gated_activation_in_the_product_epilogue(m, activation):
+    """act(x W_gate^T) * (x W_up^T) with the activation applied by the product's epilogue, for the row counts
+    of every product kernel."""
+    from hfee_b200.kernels import ops
+    rng = np.random.default_rng(m)
+    k, inner, granule = 256, 512, ops.SWIGLU_GRANULE
+    x = torch.tensor(rng.normal(size=(m, k)), dtype=torch.bfloat16, device=DEV)
+    gate = torch.tensor(rng.normal(size=(inner, k)) / 16, dtype=torch.bfloat16, device=DEV)
+    up = torch.tensor(rng.normal(size=(inner, k)) / 16, dtype=torch.bfloat16, device=DEV)
+    w = torch.stack([gate.reshape(inner // granule, granule, k), up.reshape(inner // granule, granule, k)], dim=1)
+    w = w.reshape(2 * inner, k).contiguous()
+    out = torch.empty((m, inner), dtype=torch.bfloat16, device=DEV)
+    scratch = torch.empty((m, 2 * inner), dtype=torch.bfloat16, device=DEV)
+    ops.linear_swiglu(x, w, out, granule, scratch, activation)
+    xd = x.double().cpu().numpy()
+    fn = plain.gelu_tanh if activation == "gelu_tanh" else plain.silu
+    want = fn(xd @ gate.double().cpu().numpy().T) * (xd @ up.double().cpu().numpy().T)
+    assert np.max(np.abs(out.double().cpu().numpy() - want)) < 1e-2 * np.max(np.abs(want))
+    ops.check_status()
