@@ -7,7 +7,7 @@
 // (window = 0: no window).  Nothing is normalised over the keys, so key blocks can be added in any order
 // and no running maximum is kept.
 //
-// A CTA takes SA_TOKENS consecutive tokens of one request and one key/value head: its rows are the
+// A CTA takes SA_ROWS / group consecutive tokens of one request and one key/value head: its rows are the
 // (token, query head of the group) pairs, 16 per warp.  Keys run in blocks of 64 from lo(first token) to
 // pos(last token): K rows and transposed V rows go to shared memory through the block table, scores are
 // float32 sums of bfloat16 products, the weights are computed in float32 and enter the second product as the
@@ -57,12 +57,13 @@ attention_sigmoid_mma_kernel(const bf16* __restrict__ q, long long ld_q, const b
   pdl_wait();
   pdl_launch_dependents();
 
-  for (int e = threadIdx.x; e < SA_ROWS * (HD / 2); e += SA_WARPS * 32) {
-    const int r = e / (HD / 2), d = (e % (HD / 2)) * 2;
-    uint32_t val = 0u;
+  // 16-byte accesses: a thread takes 8 consecutive dimensions of a row
+  for (int e = threadIdx.x; e < SA_ROWS * (HD / 8); e += SA_WARPS * 32) {
+    const int r = e / (HD / 8), d = (e % (HD / 8)) * 8;
+    uint4 val = make_uint4(0u, 0u, 0u, 0u);
     if (r < rows)
-      val = *reinterpret_cast<const uint32_t*>(q + (long long)(begin + tok0 + r / group) * ld_q + (long long)(kvh * group + r % group) * HD + d);
-    *reinterpret_cast<uint32_t*>(qs + r * LDD + d) = val;
+      val = *reinterpret_cast<const uint4*>(q + (long long)(begin + tok0 + r / group) * ld_q + (long long)(kvh * group + r % group) * HD + d);
+    *reinterpret_cast<uint4*>(qs + r * LDD + d) = val;
   }
   // positions and visibility of this thread's rows: r0 + g and r0 + g + 8
   const int r0 = warp * 16;
@@ -90,18 +91,18 @@ attention_sigmoid_mma_kernel(const bf16* __restrict__ q, long long ld_q, const b
 
   for (int kb = key_lo; kb <= p_last; kb += SA_KEYS) {
     __syncthreads();                                    // the block before is used up (and qs is written)
-    for (int e = threadIdx.x; e < SA_KEYS * (HD / 2); e += SA_WARPS * 32) {
-      const int j = e / (HD / 2), d = (e % (HD / 2)) * 2;
-      uint32_t kv = 0u, vv = 0u;
+    for (int e = threadIdx.x; e < SA_KEYS * (HD / 8); e += SA_WARPS * 32) {
+      const int j = e % SA_KEYS, d = (e / SA_KEYS) * 8;      // neighbouring threads: neighbouring keys (transposed stores meet no bank twice)
+      uint4 kv = make_uint4(0u, 0u, 0u, 0u), vv = make_uint4(0u, 0u, 0u, 0u);
       if (kb + j <= p_last) {
         const long long at = paged_offset(cache, slot, kb + j, kvh) + d;
-        kv = *reinterpret_cast<const uint32_t*>(k_pool + at);
-        vv = *reinterpret_cast<const uint32_t*>(v_pool + at);
+        kv = *reinterpret_cast<const uint4*>(k_pool + at);
+        vv = *reinterpret_cast<const uint4*>(v_pool + at);
       }
-      *reinterpret_cast<uint32_t*>(ks + j * LDD + d) = kv;
-      const __nv_bfloat162 v2 = *reinterpret_cast<const __nv_bfloat162*>(&vv);
-      vt[d * LDK + j] = v2.x;
-      vt[(d + 1) * LDK + j] = v2.y;
+      *reinterpret_cast<uint4*>(ks + j * LDD + d) = kv;
+      const bf16* v8 = reinterpret_cast<const bf16*>(&vv);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) vt[(d + i) * LDK + j] = v8[i];
     }
     __syncthreads();
     if (r0 < rows) {
@@ -113,10 +114,11 @@ attention_sigmoid_mma_kernel(const bf16* __restrict__ q, long long ld_q, const b
         uint32_t a[4];
         load_a(a, qs, LDD, r0, kk, lane);
 #pragma unroll
-        for (int nt = 0; nt < SA_KEYS / 8; ++nt) {
-          uint32_t b0, b1;
-          load_b(b0, b1, ks, LDD, nt * 8, kk, lane);
-          mma_bf16(acc_s[nt], a, b0, b1);
+        for (int nt = 0; nt < SA_KEYS / 8; nt += 2) {
+          uint32_t b[4];
+          load_b_pair(b, ks, LDD, nt * 8, kk, lane);
+          mma_bf16(acc_s[nt], a, b[0], b[1]);
+          mma_bf16(acc_s[nt + 1], a, b[2], b[3]);
         }
       }
 #pragma unroll
@@ -137,11 +139,13 @@ attention_sigmoid_mma_kernel(const bf16* __restrict__ q, long long ld_q, const b
         load_a(ah, p_hi, LDK, r0, ks16 * 16, lane);
         load_a(al, p_lo, LDK, r0, ks16 * 16, lane);
 #pragma unroll
-        for (int nt = 0; nt < NT; ++nt) {
-          uint32_t b0, b1;
-          load_b(b0, b1, vt, LDK, nt * 8, ks16 * 16, lane);
-          mma_bf16(acc_o[nt], ah, b0, b1);
-          mma_bf16(acc_o[nt], al, b0, b1);
+        for (int nt = 0; nt < NT; nt += 2) {
+          uint32_t b[4];
+          load_b_pair(b, vt, LDK, nt * 8, ks16 * 16, lane);
+          mma_bf16(acc_o[nt], ah, b[0], b[1]);
+          mma_bf16(acc_o[nt], al, b[0], b[1]);
+          mma_bf16(acc_o[nt + 1], ah, b[2], b[3]);
+          mma_bf16(acc_o[nt + 1], al, b[2], b[3]);
         }
       }
       __syncwarp();
@@ -204,9 +208,9 @@ HFEE_API int hfee_attention_sigmoid_mma(const void* q, long long ld_q, const voi
   if (n_tokens == 0 || requests == 0) return HFEE_OK;
   HFEE_REQUIRE(hfee_attention_sigmoid_mma_supports(heads, kv_heads, head_dim),
                "attention_sigmoid_mma: heads %d, kv_heads %d, head_dim %d are not sizes of this kernel", heads, kv_heads, head_dim);
-  HFEE_REQUIRE(ld_q % 2 == 0 && ld_o % 2 == 0 && (gate == nullptr || ld_gate % 2 == 0) &&
-               (uintptr_t)q % 4 == 0 && (uintptr_t)out % 4 == 0 && (uintptr_t)gate % 4 == 0,
-               "attention_sigmoid_mma: rows must start on 4-byte boundaries");
+  HFEE_REQUIRE(ld_q % 8 == 0 && (uintptr_t)q % 16 == 0, "attention_sigmoid_mma: query rows must start on 16-byte boundaries");
+  HFEE_REQUIRE(ld_o % 2 == 0 && (gate == nullptr || ld_gate % 2 == 0) && (uintptr_t)out % 4 == 0 && (uintptr_t)gate % 4 == 0,
+               "attention_sigmoid_mma: output and gate rows must start on 4-byte boundaries");
   HFEE_REQUIRE(window >= 0 && chunk >= 0, "attention_sigmoid_mma: bad mask option");
   PagedCache c;
   HFEE_REQUIRE(make_paged_cache(&c, block_table, max_pages, page_size, kv_heads, head_dim),

@@ -117,6 +117,66 @@ norm_gate_kernel(const float* __restrict__ x, long long ld_x, const float* __res
   }
 }
 
+// four consecutive activations at once (rows that 8- or 16-byte accesses can read)
+__device__ __forceinline__ float4 load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 load4(const __nv_bfloat16* p) {
+  const uint2 raw = *reinterpret_cast<const uint2*>(p);
+  const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&raw.x), b = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+  return make_float4(__bfloat162float(a.x), __bfloat162float(a.y), __bfloat162float(b.x), __bfloat162float(b.y));
+}
+__device__ __forceinline__ void store4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void store4(__nv_bfloat16* p, float4 v) {
+  const __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+  uint2 raw;
+  raw.x = *reinterpret_cast<const uint32_t*>(&a);
+  raw.y = *reinterpret_cast<const uint32_t*>(&b);
+  *reinterpret_cast<uint2*>(p) = raw;
+}
+
+// norm_gate for widths that are multiples of 4 and at most ROW_THREADS * 4 * NCH, the row kept in registers
+template <typename T, int NCH>
+__global__ void __launch_bounds__(ROW_THREADS)
+norm_gate_vec_kernel(const float* __restrict__ x, long long ld_x, const float* __restrict__ w, float eps,
+                     const T* __restrict__ gate, long long ld_g, T* __restrict__ out, long long ld_o, int width) {
+  __shared__ float partial[ROW_THREADS / 32];
+  float4 wv[NCH];
+#pragma unroll
+  for (int j = 0; j < NCH; ++j) {
+    const int c = (threadIdx.x + j * ROW_THREADS) * 4;
+    wv[j] = (w != nullptr && c < width) ? __ldg(reinterpret_cast<const float4*>(w + c)) : make_float4(1.f, 1.f, 1.f, 1.f);
+  }
+  pdl_wait();
+  pdl_launch_dependents();
+  const float* xr = x + (long long)blockIdx.x * ld_x;
+  const T* gr = gate + (long long)blockIdx.x * ld_g;
+  T* orow = out + (long long)blockIdx.x * ld_o;
+  float4 xv[NCH], gv[NCH];
+#pragma unroll
+  for (int j = 0; j < NCH; ++j) {
+    const int c = (threadIdx.x + j * ROW_THREADS) * 4;
+    xv[j] = c < width ? load4(xr + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+    gv[j] = c < width ? load4(gr + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  float scale = 1.f;
+  if (w != nullptr) {
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < NCH; ++j) ss = fmaf(xv[j].x, xv[j].x, fmaf(xv[j].y, xv[j].y, fmaf(xv[j].z, xv[j].z, fmaf(xv[j].w, xv[j].w, ss))));
+    scale = 1.0f / sqrtf(block_sum(ss, partial) / (float)width + eps);
+  }
+#pragma unroll
+  for (int j = 0; j < NCH; ++j) {
+    const int c = (threadIdx.x + j * ROW_THREADS) * 4;
+    if (c >= width) continue;
+    float4 o;
+    o.x = xv[j].x * scale * wv[j].x * sigmoid_f32(gv[j].x);
+    o.y = xv[j].y * scale * wv[j].y * sigmoid_f32(gv[j].y);
+    o.z = xv[j].z * scale * wv[j].z * sigmoid_f32(gv[j].z);
+    o.w = xv[j].w * scale * wv[j].w * sigmoid_f32(gv[j].w);
+    store4(orow + c, o);
+  }
+}
+
 enum GateActivation { GA_SILU = 0, GA_GELU_TANH = 1 };
 
 __device__ __forceinline__ float gate_activation(float z, int act) {
@@ -244,12 +304,23 @@ HFEE_API int hfee_norm_gate(const float* x, long long ld_x, const float* w, floa
                             void* out, long long ld_o, int n, int width, int dtype, cudaStream_t stream) {
   if (n == 0) return HFEE_OK;
   HFEE_REQUIRE(n > 0 && width > 0 && ld_x >= width && ld_g >= width && ld_o >= width, "norm_gate: bad sizes");
-  if (dtype == HFEE_F32)
-    hfee_launch(norm_gate_kernel<float>, dim3(n), dim3(ROW_THREADS), 0, stream, x, ld_x, w, eps, (const float*)gate, ld_g, (float*)out, ld_o, width);
-  else if (dtype == HFEE_BF16)
-    hfee_launch(norm_gate_kernel<__nv_bfloat16>, dim3(n), dim3(ROW_THREADS), 0, stream, x, ld_x, w, eps, (const __nv_bfloat16*)gate, ld_g, (__nv_bfloat16*)out, ld_o, width);
-  else
-    return hfee_fail(HFEE_ERR_ARG, "norm_gate: unknown dtype %d", dtype);
+  const size_t elem = dtype == HFEE_F32 ? 4 : 2;
+  const bool vec = width % 4 == 0 && ld_x % 4 == 0 && ld_g % 4 == 0 && ld_o % 4 == 0 && (uintptr_t)x % 16 == 0 &&
+                   (w == nullptr || (uintptr_t)w % 16 == 0) && (uintptr_t)gate % (4 * elem) == 0 &&
+                   (uintptr_t)out % (4 * elem) == 0 && width <= ROW_THREADS * 4 * 8;
+#define HFEE_NG(T)                                                                                                        \
+  do {                                                                                                                    \
+    if (vec && width <= ROW_THREADS * 4 * 2)                                                                              \
+      hfee_launch(norm_gate_vec_kernel<T, 2>, dim3(n), dim3(ROW_THREADS), 0, stream, x, ld_x, w, eps, (const T*)gate, ld_g, (T*)out, ld_o, width); \
+    else if (vec)                                                                                                         \
+      hfee_launch(norm_gate_vec_kernel<T, 8>, dim3(n), dim3(ROW_THREADS), 0, stream, x, ld_x, w, eps, (const T*)gate, ld_g, (T*)out, ld_o, width); \
+    else                                                                                                                  \
+      hfee_launch(norm_gate_kernel<T>, dim3(n), dim3(ROW_THREADS), 0, stream, x, ld_x, w, eps, (const T*)gate, ld_g, (T*)out, ld_o, width);        \
+  } while (0)
+  if (dtype == HFEE_F32) HFEE_NG(float);
+  else if (dtype == HFEE_BF16) HFEE_NG(__nv_bfloat16);
+  else return hfee_fail(HFEE_ERR_ARG, "norm_gate: unknown dtype %d", dtype);
+#undef HFEE_NG
   return hfee_check_launch("norm_gate");
 }
 

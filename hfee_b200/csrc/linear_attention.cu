@@ -308,8 +308,9 @@ la_mma_sums_kernel(const bf16* __restrict__ k, const bf16* __restrict__ v, long 
   __syncthreads();
   // 16-byte loads: a thread takes 8 consecutive dimensions of one token
   const int dv = dim / 8;
+  // neighbouring threads take neighbouring tokens, so that the transposed stores meet no bank twice
   for (int e = threadIdx.x; e < LM_T * dv; e += LM_WARPS * 32) {
-    const int s = e / dv, d = (e % dv) * 8;
+    const int s = e % LM_T, d = (e / LM_T) * 8;
     Pack8 raw = {};
     if (s < n) raw = *reinterpret_cast<const Pack8*>(k + (long long)(begin + t0 + s) * ld + (long long)head * dim + d);
     const float w = s < n ? pw[n - 1 - s] : 0.f;
@@ -320,7 +321,7 @@ la_mma_sums_kernel(const bf16* __restrict__ k, const bf16* __restrict__ v, long 
     }
   }
   for (int e = threadIdx.x; e < LM_T * (LM_COLS / 8); e += LM_WARPS * 32) {
-    const int s = e / (LM_COLS / 8), j = (e % (LM_COLS / 8)) * 8, c = c0 + j;
+    const int s = e % LM_T, j = (e / LM_T) * 8, c = c0 + j;
     Pack8 raw = {};
     if (s < n && c < vdim) raw = *reinterpret_cast<const Pack8*>(v + (long long)(begin + t0 + s) * ld + (long long)head * vdim + c);
 #pragma unroll
@@ -339,11 +340,13 @@ la_mma_sums_kernel(const bf16* __restrict__ k, const bf16* __restrict__ v, long 
       load_a(ah, kt_hi, LDT, d0, ks * 16, lane);
       load_a(al, kt_lo, LDT, d0, ks * 16, lane);
 #pragma unroll
-      for (int nt = 0; nt < LM_COLS / 8; ++nt) {
-        uint32_t b0, b1;
-        load_b(b0, b1, vt, LDT, nt * 8, ks * 16, lane);
-        mma_bf16(acc[nt], ah, b0, b1);
-        mma_bf16(acc[nt], al, b0, b1);
+      for (int nt = 0; nt < LM_COLS / 8; nt += 2) {
+        uint32_t b[4];
+        load_b_pair(b, vt, LDT, nt * 8, ks * 16, lane);
+        mma_bf16(acc[nt], ah, b[0], b[1]);
+        mma_bf16(acc[nt], al, b[0], b[1]);
+        mma_bf16(acc[nt + 1], ah, b[2], b[3]);
+        mma_bf16(acc[nt + 1], al, b[2], b[3]);
       }
     }
 #pragma unroll
@@ -404,7 +407,7 @@ la_mma_out_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, const 
     *reinterpret_cast<Pack8*>(ks_ + s * LDD + d) = ok;
   }
   for (int e = threadIdx.x; e < LM_T * (LM_COLS / 8); e += LM_WARPS * 32) {
-    const int s = e / (LM_COLS / 8), j = (e % (LM_COLS / 8)) * 8, c = c0 + j;
+    const int s = e % LM_T, j = (e / LM_T) * 8, c = c0 + j;
     Pack8 raw = {};
     if (s < n && c < vdim) raw = *reinterpret_cast<const Pack8*>(v + (long long)(begin + t0 + s) * ld + (long long)head * vdim + c);
 #pragma unroll
@@ -412,7 +415,7 @@ la_mma_out_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, const 
   }
   const float* S_in = sums + (((long long)blockIdx.y * heads + head) * dim) * vdim;
   for (int e = threadIdx.x; e < dim * (LM_COLS / 4); e += LM_WARPS * 32) {
-    const int d = e / (LM_COLS / 4), j = (e % (LM_COLS / 4)) * 4, c = c0 + j;
+    const int d = e % dim, j = (e / dim) * 4, c = c0 + j;       // neighbouring threads: neighbouring state rows
     float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
     if (c < vdim) x = *reinterpret_cast<const float4*>(S_in + (long long)d * vdim + c);
     split_bf16(x.x, &st_hi[(j + 0) * LDD + d], &st_lo[(j + 0) * LDD + d]);
@@ -435,11 +438,12 @@ la_mma_out_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, const 
     uint32_t a[4];
     load_a(a, qs, LDD, r0, kk, lane);
 #pragma unroll
-    for (int nt = 0; nt < LM_T / 8; ++nt) {
-      if (nt < key_tiles) {
-        uint32_t b0, b1;
-        load_b(b0, b1, ks_, LDD, nt * 8, kk, lane);
-        mma_bf16(acc[nt], a, b0, b1);
+    for (int nt = 0; nt < LM_T / 8; nt += 2) {
+      if (nt < key_tiles) {                                // key_tiles is even
+        uint32_t b[4];
+        load_b_pair(b, ks_, LDD, nt * 8, kk, lane);
+        mma_bf16(acc[nt], a, b[0], b[1]);
+        mma_bf16(acc[nt + 1], a, b[2], b[3]);
       }
     }
   }
@@ -465,23 +469,27 @@ la_mma_out_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, const 
     load_a(ah, p_hi, LDT, r0, ks * 16, lane);
     load_a(al, p_lo, LDT, r0, ks * 16, lane);
 #pragma unroll
-    for (int nt = 0; nt < LM_COLS / 8; ++nt) {
-      uint32_t b0, b1;
-      load_b(b0, b1, vt, LDT, nt * 8, ks * 16, lane);
-      mma_bf16(acc[nt], ah, b0, b1);
-      mma_bf16(acc[nt], al, b0, b1);
+    for (int nt = 0; nt < LM_COLS / 8; nt += 2) {
+      uint32_t b[4];
+      load_b_pair(b, vt, LDT, nt * 8, ks * 16, lane);
+      mma_bf16(acc[nt], ah, b[0], b[1]);
+      mma_bf16(acc[nt], al, b[0], b[1]);
+      mma_bf16(acc[nt + 1], ah, b[2], b[3]);
+      mma_bf16(acc[nt + 1], al, b[2], b[3]);
     }
   }
   for (int kk = 0; kk < dim; kk += 16) {
     uint32_t a[4];
     load_a(a, qs, LDD, r0, kk, lane);
 #pragma unroll
-    for (int nt = 0; nt < LM_COLS / 8; ++nt) {
-      uint32_t b0, b1;
-      load_b(b0, b1, st_hi, LDD, nt * 8, kk, lane);
-      mma_bf16(acc_s[nt], a, b0, b1);
-      load_b(b0, b1, st_lo, LDD, nt * 8, kk, lane);
-      mma_bf16(acc_s[nt], a, b0, b1);
+    for (int nt = 0; nt < LM_COLS / 8; nt += 2) {
+      uint32_t bh[4], bl[4];
+      load_b_pair(bh, st_hi, LDD, nt * 8, kk, lane);
+      load_b_pair(bl, st_lo, LDD, nt * 8, kk, lane);
+      mma_bf16(acc_s[nt], a, bh[0], bh[1]);
+      mma_bf16(acc_s[nt], a, bl[0], bl[1]);
+      mma_bf16(acc_s[nt + 1], a, bh[2], bh[3]);
+      mma_bf16(acc_s[nt + 1], a, bl[2], bl[3]);
     }
   }
 #pragma unroll

@@ -11,13 +11,23 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], 
                : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
-// rows r0..r0+15, columns k0..k0+15 of a row-major matrix in shared memory, as the A operand
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const bf16* row) {
+  const uint32_t addr = (uint32_t)__cvta_generic_to_shared(row);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+// rows r0..r0+15, columns k0..k0+15 of a row-major matrix in shared memory, as the A operand: one ldmatrix of
+// four 8 x 8 pieces (rows 0-7 / 8-15 times columns 0-7 / 8-15; lane l names row l % 8 of piece l / 8).  Rows
+// must start on 16-byte boundaries (ld and k0 multiples of 8).
 __device__ __forceinline__ void load_a(uint32_t (&a)[4], const bf16* A, int ld, int r0, int k0, int lane) {
-  const bf16* p = A + (r0 + (lane >> 2)) * ld + k0 + 2 * (lane & 3);
-  a[0] = *reinterpret_cast<const uint32_t*>(p);
-  a[1] = *reinterpret_cast<const uint32_t*>(p + 8 * ld);
-  a[2] = *reinterpret_cast<const uint32_t*>(p + 8);
-  a[3] = *reinterpret_cast<const uint32_t*>(p + 8 * ld + 8);
+  const int piece = lane >> 3, r = lane & 7;
+  ldmatrix_x4(a, A + (r0 + r + (piece & 1) * 8) * ld + k0 + (piece >> 1) * 8);
+}
+// the B operands of two neighbouring tiles of output columns, n0..n0+7 (b[0], b[1]) and n0+8..n0+15 (b[2], b[3]),
+// from Bt[n][k] (the operand transposed, row-major), by one ldmatrix
+__device__ __forceinline__ void load_b_pair(uint32_t (&b)[4], const bf16* Bt, int ld, int n0, int k0, int lane) {
+  const int piece = lane >> 3, r = lane & 7;
+  ldmatrix_x4(b, Bt + (n0 + r + (piece >> 1) * 8) * ld + k0 + (piece & 1) * 8);
 }
 // the B operand for output columns n0..n0+7 from Bt[n][k] (the operand transposed, row-major)
 __device__ __forceinline__ void load_b(uint32_t& b0, uint32_t& b1, const bf16* Bt, int ld, int n0, int k0, int lane) {

@@ -8,6 +8,8 @@ where that matters, and prints what it achieved against the roofline that bounds
     python -m hfee_b200.kernels.microbench gemm_skinny  --m 64 --n 2048 --k 8192 --epilogue accum
     python -m hfee_b200.kernels.microbench attention_decode  --batch 8 --context 2048 --heads 32 --kv-heads 8 --head-dim 64
     python -m hfee_b200.kernels.microbench attention_prefill --tokens 2048 --heads 32 --kv-heads 8 --head-dim 64
+    python -m hfee_b200.kernels.microbench sigmoid_attention --tokens 2048 --heads 32 --kv-heads 8 --head-dim 64 --chunk 128
+    python -m hfee_b200.kernels.microbench linear_attention  --tokens 2048 --heads 32 --head-dim 64 [--batch 8 for a decode step]
 
 ``--iters`` timed launches follow ``--warmup`` untimed ones; ``--rotate`` distinct weight
 buffers are cycled so that a weight-streaming kernel never finds its weights in L2.  The
@@ -128,9 +130,69 @@ def _attention(args, decode: bool) -> dict:
             "kv_gbs": round(kv_bytes / sec / 1e9, 1), "tflops": round(flops / sec / 1e12, 1)}
 
 
+def _batch_of(before, new):
+    b = _Batch()
+    cu = [0]
+    for x in new:
+        cu.append(cu[-1] + x)
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    b.cu_tokens, b.slots, b.context_before = i32(cu), i32(list(range(len(new)))), i32(before)
+    b.n, b.r, b.max_new, b.max_context = sum(new), len(new), max(new), max(s + c for s, c in zip(before, new))
+    b.positions = i32([p for s, c in zip(before, new) for p in range(s, s + c)])
+    b.slot_of_token = i32([i for i, c in enumerate(new) for _ in range(c)])
+    return b
+
+
+def _sigmoid_attention(args) -> dict:
+    """Chunked sigmoid attention of one prompt portion (``--batch 0``) or of a decode step of ``--batch`` requests."""
+    heads, kv, hd, page, chunk = args.heads, args.kv_heads, args.head_dim, args.page_size, args.chunk
+    before, new = ([args.context] * args.batch, [1] * args.batch) if args.decode else ([args.context_before], [args.tokens])
+    b = _batch_of(before, new)
+    max_pages = -(-b.max_context // page)
+    table = torch.randperm(b.r * max_pages).reshape(b.r, max_pages).to(torch.int32).to(DEV)
+    kp = torch.randn(b.r * max_pages, kv, page, hd, device=DEV).to(torch.bfloat16)
+    vp = torch.randn(b.r * max_pages, kv, page, hd, device=DEV).to(torch.bfloat16)
+    q = torch.randn(b.n, heads * hd, device=DEV).to(torch.bfloat16)
+    gate = torch.randn(b.n, heads * hd, device=DEV).to(torch.bfloat16)
+    out = torch.empty_like(q)
+    temp = torch.ones(heads, device=DEV)
+    bias = torch.zeros(heads, device=DEV)
+    ops.USE_SIGMOID_MMA = not args.no_tc_attention
+    fn = lambda i: ops.sigmoid_attention(q, kp, vp, table, page, b, out, heads, kv, hd, hd ** -0.5, 0, chunk, temp, bias, gate)
+    sec = _time(fn, args.warmup, args.iters)
+    keys = sum(p - (p // chunk) * chunk + 1 if chunk else p + 1 for s, c in zip(before, new) for p in range(s, s + c))
+    flops = 4.0 * heads * hd * keys
+    moved = 3 * b.n * heads * hd * 2 + 2 * sum(min(s + c, (chunk or s + c) + c) for s, c in zip(before, new)) * kv * hd * 2
+    return {"kernel": "sigmoid_attention", "heads": heads, "kv_heads": kv, "head_dim": hd, "chunk": chunk, "requests": b.r,
+            "tokens": b.n, "us": round(sec * 1e6, 2), "tflops": round(flops / sec / 1e12, 2), "gbs": round(moved / sec / 1e9, 1)}
+
+
+def _linear_attention(args) -> dict:
+    """Linear attention with decay: one prompt portion through the chunked kernels, or a decode step of ``--batch``
+    requests through the token-by-token kernel (key and value size ``--head-dim``)."""
+    heads, d = args.heads, args.head_dim
+    before, new = ([args.context] * args.batch, [1] * args.batch) if args.decode else ([0], [args.tokens])
+    b = _batch_of(before, new)
+    proj = (torch.randn(b.n, 4 * heads * d, device=DEV) * 0.5).to(torch.bfloat16)
+    q, k, v = proj[:, :heads * d], proj[:, heads * d:2 * heads * d], proj[:, 2 * heads * d:3 * heads * d]
+    decay = torch.linspace(0.5, 0.999, heads, device=DEV)
+    state = torch.zeros(b.r, heads, d, d, device=DEV)
+    out = torch.empty(b.n, heads * d, dtype=torch.float32, device=DEV)
+    ws = torch.empty(ops.linear_attention_workspace(b.r, b.n, heads, d, d), dtype=torch.float32, device=DEV)
+    fn = lambda i: ops.linear_attention(q, k, v, decay, state, b, out, heads, d, d, "silu", True, ws,
+                                        tensor_cores=not args.no_tc_attention)
+    sec = _time(fn, args.warmup, args.iters)
+    state_bytes = b.r * heads * d * d * 4
+    moved = 3 * b.n * heads * d * 2 + b.n * heads * d * 4 + 2 * state_bytes        # q, k, v in; o out; the state in and out
+    flops = b.n * heads * 4.0 * d * d if args.decode else b.n * heads * (4.0 * d * d + 4.0 * d * 32)
+    return {"kernel": "linear_attention", "heads": heads, "dim": d, "requests": b.r, "tokens": b.n,
+            "us": round(sec * 1e6, 2), "tflops": round(flops / sec / 1e12, 2), "gbs": round(moved / sec / 1e9, 1)}
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("kernel", choices=["gemm_tcgen05", "gemm_stream", "gemm_skinny", "gemm_ring", "gemm_pair", "attention_decode", "attention_prefill"])
+    ap.add_argument("kernel", choices=["gemm_tcgen05", "gemm_stream", "gemm_skinny", "gemm_ring", "gemm_pair", "attention_decode", "attention_prefill",
+                                      "sigmoid_attention", "linear_attention"])
     ap.add_argument("--m", type=int, default=2048)
     ap.add_argument("--n", type=int, default=16384)
     ap.add_argument("--k", type=int, default=2048)
@@ -146,6 +208,8 @@ def main(argv=None) -> int:
     ap.add_argument("--head-dim", type=int, default=64)
     ap.add_argument("--page-size", type=int, default=64)
     ap.add_argument("--splits", type=int, default=0)
+    ap.add_argument("--chunk", type=int, default=128, help="sigmoid_attention: positions per block of the mask")
+    ap.add_argument("--decode", action="store_true", help="sigmoid_attention / linear_attention: a decode step of --batch requests")
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--tc-attention", action="store_true", help="attention_prefill: the tcgen05 kernel (the default)")
@@ -158,6 +222,10 @@ def main(argv=None) -> int:
     torch.manual_seed(0)
     if args.kernel.startswith("gemm"):
         res = _gemm(args, args.kernel)
+    elif args.kernel == "sigmoid_attention":
+        res = _sigmoid_attention(args)
+    elif args.kernel == "linear_attention":
+        res = _linear_attention(args)
     else:
         res = _attention(args, args.kernel == "attention_decode")
     print(json.dumps(res))

@@ -913,7 +913,7 @@ def sigmoid_attention(q, k_pool, v_pool, block_table, page_size, step, out, head
     sizes: bfloat16 with a head size and a group the tensor-core kernel is built for runs there (prompt portions
     and decode steps alike), everything else on the CUDA cores in float32."""
     if USE_SIGMOID_MMA and q.dtype == torch.bfloat16 and sigmoid_mma_supports(heads, kv_heads, head_dim) and (
-            _rows(q, "q") % 2 == 0 and _rows(out, "out") % 2 == 0 and (gate is None or (_rows(gate, "gate") % 2 == 0
+            _rows(q, "q") % 8 == 0 and q.data_ptr() % 16 == 0 and _rows(out, "out") % 2 == 0 and (gate is None or (_rows(gate, "gate") % 2 == 0
                                                                                      and gate.data_ptr() % 4 == 0))):
         lib = library()
         for t, what in ((block_table, "block_table"), (step.cu_tokens, "cu_tokens"), (step.slots, "slots"),

@@ -128,9 +128,17 @@ def test_row_kernels(dtype):
         assert np.max(np.abs(r_d.cpu().numpy() - (rw + plain.rms_norm(yw, ww, 1e-3)))) < 2e-5
         assert torch.equal(cast, r_d.to(dtype))
 
+    tol = 1e-5 if dtype == torch.float32 else 1e-2
+    for wide in (2048, 4096, 4098):                   # 16-byte variants and the plain kernel; the gate a column slice
+        xw, ww = rng.normal(size=(3, wide)) * 2, 1 + rng.normal(size=wide) * 0.3
+        both = torch.tensor(rng.normal(size=(3, 2 * wide)), dtype=dtype, device=DEV)
+        gw, ow = both[:, wide:], torch.empty((3, wide), dtype=dtype, device=DEV)
+        ops.norm_gate(torch.tensor(xw, dtype=torch.float32, device=DEV), torch.tensor(ww, dtype=torch.float32, device=DEV), 1e-3, gw, ow)
+        want = plain.rms_norm(xw, ww, 1e-3) * plain.sigmoid(gw.double().cpu().numpy())
+        assert np.max(np.abs(ow.double().cpu().numpy() - want)) < tol * np.max(np.abs(want))
+
     g = torch.tensor(rng.normal(size=(n, width)), dtype=dtype, device=DEV)
     out = torch.empty((n, width), dtype=dtype, device=DEV)
-    tol = 1e-5 if dtype == torch.float32 else 1e-2
     for weight in (torch.tensor(w, dtype=torch.float32, device=DEV), None):
         ops.norm_gate(torch.tensor(y, dtype=torch.float32, device=DEV), weight, 1e-3, g, out)
         want = (plain.rms_norm(y, w, 1e-3) if weight is not None else y) * plain.sigmoid(g.double().cpu().numpy())
