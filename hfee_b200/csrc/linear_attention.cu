@@ -191,6 +191,7 @@ __global__ void la_chunk_scan_kernel(const float* __restrict__ decay, const int*
   const float lam = decay[head];
   const int runs = runs_of<RUN>(count);
   const float lam_full = powf(lam, (float)RUN);
+  const float lam_last = powf(lam, (float)(count - (runs - 1) * RUN));      // only the last run can be short
   const long long per = (long long)dim * vdim;
   float* S_g = state + ((long long)slot * heads + head) * per;
   for (long long e = (long long)blockIdx.z * blockDim.x + threadIdx.x; e < per; e += (long long)gridDim.z * blockDim.x) {
@@ -205,9 +206,8 @@ __global__ void la_chunk_scan_kernel(const float* __restrict__ decay, const int*
       for (int i = 0; i < 8; ++i) {
         const int run = base + i;
         if (run < runs) {
-          const int n = min(RUN, count - run * RUN);
           A0[run * stride] = S;
-          S = fmaf(n == RUN ? lam_full : powf(lam, (float)n), S, own[i]);
+          S = fmaf(run == runs - 1 ? lam_last : lam_full, S, own[i]);
         }
       }
     }
@@ -309,23 +309,41 @@ la_mma_sums_kernel(const bf16* __restrict__ k, const bf16* __restrict__ v, long 
   // 16-byte loads: a thread takes 8 consecutive dimensions of one token
   const int dv = dim / 8;
   // neighbouring threads take neighbouring tokens, so that the transposed stores meet no bank twice
-  for (int e = threadIdx.x; e < LM_T * dv; e += LM_WARPS * 32) {
-    const int s = e % LM_T, d = (e / LM_T) * 8;
-    Pack8 raw = {};
-    if (s < n) raw = *reinterpret_cast<const Pack8*>(k + (long long)(begin + t0 + s) * ld + (long long)head * dim + d);
-    const float w = s < n ? pw[n - 1 - s] : 0.f;
+  // the values' loads first (a fixed number per thread), then the keys' in batches of four: all of a batch's
+  // loads are requested before the first is used
+  constexpr int V_PER = LM_T * (LM_COLS / 8) / (LM_WARPS * 32);
+  Pack8 rv[V_PER];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const float kb = __bfloat162float(__float2bfloat16_rn(activate<ACT>(__bfloat162float(raw.v[i]))));
-      split_bf16(kb * w, &kt_hi[(d + i) * LDT + s], &kt_lo[(d + i) * LDT + s]);
+  for (int i = 0; i < V_PER; ++i) {
+    const int e = threadIdx.x + i * LM_WARPS * 32, s = e % LM_T, c = c0 + (e / LM_T) * 8;
+    rv[i] = Pack8{};
+    if (s < n && c < vdim) rv[i] = *reinterpret_cast<const Pack8*>(v + (long long)(begin + t0 + s) * ld + (long long)head * vdim + c);
+  }
+  for (int e0 = threadIdx.x; e0 < LM_T * dv; e0 += 4 * LM_WARPS * 32) {
+    Pack8 raw[4];
+#pragma unroll
+    for (int b = 0; b < 4; ++b) {
+      const int e = e0 + b * LM_WARPS * 32, s = e % LM_T, d = (e / LM_T) * 8;
+      raw[b] = Pack8{};
+      if (e < LM_T * dv && s < n) raw[b] = *reinterpret_cast<const Pack8*>(k + (long long)(begin + t0 + s) * ld + (long long)head * dim + d);
+    }
+#pragma unroll
+    for (int b = 0; b < 4; ++b) {
+      const int e = e0 + b * LM_WARPS * 32, s = e % LM_T, d = (e / LM_T) * 8;
+      if (e >= LM_T * dv) break;
+      const float w = s < n ? pw[n - 1 - s] : 0.f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float kb = __bfloat162float(__float2bfloat16_rn(activate<ACT>(__bfloat162float(raw[b].v[i]))));
+        split_bf16(kb * w, &kt_hi[(d + i) * LDT + s], &kt_lo[(d + i) * LDT + s]);
+      }
     }
   }
-  for (int e = threadIdx.x; e < LM_T * (LM_COLS / 8); e += LM_WARPS * 32) {
-    const int s = e % LM_T, j = (e / LM_T) * 8, c = c0 + j;
-    Pack8 raw = {};
-    if (s < n && c < vdim) raw = *reinterpret_cast<const Pack8*>(v + (long long)(begin + t0 + s) * ld + (long long)head * vdim + c);
 #pragma unroll
-    for (int i = 0; i < 8; ++i) vt[(j + i) * LDT + s] = __float2bfloat16_rn(activate<ACT>(__bfloat162float(raw.v[i])));
+  for (int i = 0; i < V_PER; ++i) {
+    const int e = threadIdx.x + i * LM_WARPS * 32, s = e % LM_T, j = (e / LM_T) * 8;
+#pragma unroll
+    for (int x = 0; x < 8; ++x) vt[(j + x) * LDT + s] = __float2bfloat16_rn(activate<ACT>(__bfloat162float(rv[i].v[x])));
   }
   __syncthreads();
   float* A = sums + (((long long)blockIdx.y * heads + head) * dim) * vdim;
@@ -387,41 +405,69 @@ la_mma_out_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, const 
   bf16* p_hi = vt + LM_COLS * LDT;                       // [LM_T][LDT]
   bf16* p_lo = p_hi + LM_T * LDT;
   float* pw = reinterpret_cast<float*>(p_lo + LM_T * LDT);   // decay^i, i = 0..LM_T
-  // 16-byte loads: a thread takes 8 consecutive dimensions of one token (4 columns of one state row)
+  // 16-byte loads: a thread takes 8 consecutive dimensions of one token (4 columns of one state row).  The values'
+  // loads go first (a fixed number per thread); queries, keys and the state follow in batches of four whose loads
+  // are all requested before the first is used.
   const int dv = dim / 8;
-  for (int e = threadIdx.x; e < LM_T * dv; e += LM_WARPS * 32) {
-    const int s = e / dv, d = (e % dv) * 8;
-    Pack8 rq = {}, rk = {};
-    if (s < n) {
-      const long long at = (long long)(begin + t0 + s) * ld + (long long)head * dim + d;
-      rq = *reinterpret_cast<const Pack8*>(q + at);
-      rk = *reinterpret_cast<const Pack8*>(k + at);
-    }
-    Pack8 oq, ok;
+  constexpr int V_PER = LM_T * (LM_COLS / 8) / (LM_WARPS * 32);
+  Pack8 rv[V_PER];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      oq.v[i] = __float2bfloat16_rn(activate<ACT>(__bfloat162float(rq.v[i])));
-      ok.v[i] = __float2bfloat16_rn(activate<ACT>(__bfloat162float(rk.v[i])));
-    }
-    *reinterpret_cast<Pack8*>(qs + s * LDD + d) = oq;
-    *reinterpret_cast<Pack8*>(ks_ + s * LDD + d) = ok;
+  for (int i = 0; i < V_PER; ++i) {
+    const int e = threadIdx.x + i * LM_WARPS * 32, s = e % LM_T, c = c0 + (e / LM_T) * 8;
+    rv[i] = Pack8{};
+    if (s < n && c < vdim) rv[i] = *reinterpret_cast<const Pack8*>(v + (long long)(begin + t0 + s) * ld + (long long)head * vdim + c);
   }
-  for (int e = threadIdx.x; e < LM_T * (LM_COLS / 8); e += LM_WARPS * 32) {
-    const int s = e % LM_T, j = (e / LM_T) * 8, c = c0 + j;
-    Pack8 raw = {};
-    if (s < n && c < vdim) raw = *reinterpret_cast<const Pack8*>(v + (long long)(begin + t0 + s) * ld + (long long)head * vdim + c);
+  for (int e0 = threadIdx.x; e0 < LM_T * dv; e0 += 4 * LM_WARPS * 32) {
+    Pack8 rq[4], rk[4];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) vt[(j + i) * LDT + s] = __float2bfloat16_rn(activate<ACT>(__bfloat162float(raw.v[i])));
+    for (int b = 0; b < 4; ++b) {
+      const int e = e0 + b * LM_WARPS * 32, s = e / dv, d = (e % dv) * 8;
+      rq[b] = Pack8{};
+      rk[b] = Pack8{};
+      if (e < LM_T * dv && s < n) {
+        const long long at = (long long)(begin + t0 + s) * ld + (long long)head * dim + d;
+        rq[b] = *reinterpret_cast<const Pack8*>(q + at);
+        rk[b] = *reinterpret_cast<const Pack8*>(k + at);
+      }
+    }
+#pragma unroll
+    for (int b = 0; b < 4; ++b) {
+      const int e = e0 + b * LM_WARPS * 32, s = e / dv, d = (e % dv) * 8;
+      if (e >= LM_T * dv) break;
+      Pack8 oq, ok;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        oq.v[i] = __float2bfloat16_rn(activate<ACT>(__bfloat162float(rq[b].v[i])));
+        ok.v[i] = __float2bfloat16_rn(activate<ACT>(__bfloat162float(rk[b].v[i])));
+      }
+      *reinterpret_cast<Pack8*>(qs + s * LDD + d) = oq;
+      *reinterpret_cast<Pack8*>(ks_ + s * LDD + d) = ok;
+    }
   }
   const float* S_in = sums + (((long long)blockIdx.y * heads + head) * dim) * vdim;
-  for (int e = threadIdx.x; e < dim * (LM_COLS / 4); e += LM_WARPS * 32) {
-    const int d = e % dim, j = (e / dim) * 4, c = c0 + j;       // neighbouring threads: neighbouring state rows
-    float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (c < vdim) x = *reinterpret_cast<const float4*>(S_in + (long long)d * vdim + c);
-    split_bf16(x.x, &st_hi[(j + 0) * LDD + d], &st_lo[(j + 0) * LDD + d]);
-    split_bf16(x.y, &st_hi[(j + 1) * LDD + d], &st_lo[(j + 1) * LDD + d]);
-    split_bf16(x.z, &st_hi[(j + 2) * LDD + d], &st_lo[(j + 2) * LDD + d]);
-    split_bf16(x.w, &st_hi[(j + 3) * LDD + d], &st_lo[(j + 3) * LDD + d]);
+  for (int e0 = threadIdx.x; e0 < dim * (LM_COLS / 4); e0 += 4 * LM_WARPS * 32) {
+    float4 x[4];
+#pragma unroll
+    for (int b = 0; b < 4; ++b) {
+      const int e = e0 + b * LM_WARPS * 32, d = e % dim, c = c0 + (e / dim) * 4;   // neighbouring threads: neighbouring state rows
+      x[b] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (e < dim * (LM_COLS / 4) && c < vdim) x[b] = *reinterpret_cast<const float4*>(S_in + (long long)d * vdim + c);
+    }
+#pragma unroll
+    for (int b = 0; b < 4; ++b) {
+      const int e = e0 + b * LM_WARPS * 32, d = e % dim, j = (e / dim) * 4;
+      if (e >= dim * (LM_COLS / 4)) break;
+      split_bf16(x[b].x, &st_hi[(j + 0) * LDD + d], &st_lo[(j + 0) * LDD + d]);
+      split_bf16(x[b].y, &st_hi[(j + 1) * LDD + d], &st_lo[(j + 1) * LDD + d]);
+      split_bf16(x[b].z, &st_hi[(j + 2) * LDD + d], &st_lo[(j + 2) * LDD + d]);
+      split_bf16(x[b].w, &st_hi[(j + 3) * LDD + d], &st_lo[(j + 3) * LDD + d]);
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < V_PER; ++i) {
+    const int e = threadIdx.x + i * LM_WARPS * 32, s = e % LM_T, j = (e / LM_T) * 8;
+#pragma unroll
+    for (int x = 0; x < 8; ++x) vt[(j + x) * LDT + s] = __float2bfloat16_rn(activate<ACT>(__bfloat162float(rv[i].v[x])));
   }
   for (int i = threadIdx.x; i <= LM_T; i += LM_WARPS * 32) pw[i] = powf(lam, (float)i);
   __syncthreads();
