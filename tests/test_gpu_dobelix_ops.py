@@ -230,14 +230,14 @@ def test_qk_norm_rope_and_sigmoid_attention(dtype, heads, kv_heads, hd, rope_dim
         assert np.max(np.abs(np.concatenate(got[i]) - want)) < tol * np.max(np.abs(want))
 
 
-@pytest.mark.parametrize("m", [1, 7, 16, 40, 300])
+@pytest.mark.parametrize("m,inner", [(1, 512), (7, 512), (16, 512), (40, 512), (300, 512), (1100, 6144)])
 @pytest.mark.parametrize("activation", ["gelu_tanh", "silu"])
-def test_gated_activation_in_the_product_epilogue(m, activation):
+def test_gated_activation_in_the_product_epilogue(m, inner, activation):
     """act(x W_gate^T) * (x W_up^T) with the activation applied by the product's epilogue, for the row counts
-    of every product kernel."""
+    of every product kernel (the last case: pairs of CTAs on tiles of 256 x 256)."""
     from hfee_b200.kernels import ops
     rng = np.random.default_rng(m)
-    k, inner, granule = 256, 512, ops.SWIGLU_GRANULE
+    k, granule = 256, ops.SWIGLU_GRANULE
     x = torch.tensor(rng.normal(size=(m, k)), dtype=torch.bfloat16, device=DEV)
     gate = torch.tensor(rng.normal(size=(inner, k)) / 16, dtype=torch.bfloat16, device=DEV)
     up = torch.tensor(rng.normal(size=(inner, k)) / 16, dtype=torch.bfloat16, device=DEV)
