@@ -12,13 +12,13 @@
 // pos(last token): K rows and transposed V rows go to shared memory through the block table, scores are
 // float32 sums of bfloat16 products, the weights are computed in float32 and enter the second product as the
 // sum of two bfloat16 numbers (the weight rounded, and what the rounding left), so that they carry 16 bits.
-// The same kernel serves prompt portions and decode steps (one token per request: one warp has rows).
+// The same kernel serves prompt portions and decode steps (one token per request: the first warps have rows).
 #include "common.cuh"
 #include "mma_tiles.cuh"
 
 namespace {
 
-constexpr int SA_ROWS = 64;       // rows of a CTA: (token, head of the group) pairs
+constexpr int SA_ROWS = 64;       // rows of a CTA: (token, head of the group) pairs (128 rows on 8 warps measured the same at head 64, slower at 128)
 constexpr int SA_WARPS = 4;
 constexpr int SA_KEYS = 64;       // keys per block
 constexpr int SA_PAD = 8;
@@ -85,6 +85,12 @@ attention_sigmoid_mma_kernel(const bf16* __restrict__ q, long long ld_q, const b
   int key_lo = chunk > 0 ? (p_first / chunk) * chunk : 0;
   if (window > 0) key_lo = max(key_lo, p_first + 1 - window);
 
+  // the keys this warp's sixteen rows can see at all: a key block outside [warp_lo, warp_hi] is skipped by the warp
+  const int warp_hi = first_pos + tok0 + min(r0 + 15, rows - 1) / group;
+  const int p_warp = first_pos + tok0 + min(r0, rows - 1) / group;
+  int warp_lo = chunk > 0 ? (p_warp / chunk) * chunk : 0;
+  if (window > 0) warp_lo = max(warp_lo, p_warp + 1 - window);
+
   float acc_o[NT][4];
 #pragma unroll
   for (int nt = 0; nt < NT; ++nt) acc_o[nt][0] = acc_o[nt][1] = acc_o[nt][2] = acc_o[nt][3] = 0.f;
@@ -105,7 +111,7 @@ attention_sigmoid_mma_kernel(const bf16* __restrict__ q, long long ld_q, const b
       for (int i = 0; i < 8; ++i) vt[(d + i) * LDK + j] = v8[i];
     }
     __syncthreads();
-    if (r0 < rows) {
+    if (r0 < rows && kb <= warp_hi && kb + SA_KEYS > warp_lo) {
       float acc_s[SA_KEYS / 8][4];
 #pragma unroll
       for (int nt = 0; nt < SA_KEYS / 8; ++nt) acc_s[nt][0] = acc_s[nt][1] = acc_s[nt][2] = acc_s[nt][3] = 0.f;
@@ -121,15 +127,24 @@ attention_sigmoid_mma_kernel(const bf16* __restrict__ q, long long ld_q, const b
           mma_bf16(acc_s[nt + 1], a, b[2], b[3]);
         }
       }
+      // sigmoid by ex2.approx and a fast division (relative error about 2^-21, far below the 16 bits the weights
+      // keep); a thread's two neighbouring keys are stored together
 #pragma unroll
       for (int nt = 0; nt < SA_KEYS / 8; ++nt) {
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const int half = i >> 1, key = kb + nt * 8 + 2 * t4 + (i & 1);
-          float w = 0.f;
-          if (key >= lo_row[half] && key <= pos_row[half]) w = 1.f / (1.f + expf(-(acc_s[nt][i] * hs[half] + hb[half])));
-          const int at = (r0 + g + 8 * half) * LDK + nt * 8 + 2 * t4 + (i & 1);
-          split_bf16(w, &p_hi[at], &p_lo[at]);
+        for (int half = 0; half < 2; ++half) {
+          float w[2];
+#pragma unroll
+          for (int j = 0; j < 2; ++j) {
+            const int key = kb + nt * 8 + 2 * t4 + j;
+            w[j] = (key >= lo_row[half] && key <= pos_row[half])
+                       ? __fdividef(1.f, 1.f + __expf(-fmaf(acc_s[nt][2 * half + j], hs[half], hb[half]))) : 0.f;
+          }
+          const __nv_bfloat162 hi = __floats2bfloat162_rn(w[0], w[1]);
+          const __nv_bfloat162 lo = __floats2bfloat162_rn(w[0] - __bfloat162float(hi.x), w[1] - __bfloat162float(hi.y));
+          const int at = (r0 + g + 8 * half) * LDK + nt * 8 + 2 * t4;
+          *reinterpret_cast<__nv_bfloat162*>(p_hi + at) = hi;
+          *reinterpret_cast<__nv_bfloat162*>(p_lo + at) = lo;
         }
       }
       __syncwarp();
@@ -164,8 +179,9 @@ attention_sigmoid_mma_kernel(const bf16* __restrict__ q, long long ld_q, const b
       const int d = nt * 8 + 2 * t4;
       float o0 = acc_o[nt][2 * half], o1 = acc_o[nt][2 * half + 1];
       if (grow != nullptr) {
-        o0 *= 1.f / (1.f + expf(-__bfloat162float(grow[d])));
-        o1 *= 1.f / (1.f + expf(-__bfloat162float(grow[d + 1])));
+        const __nv_bfloat162 g2 = *reinterpret_cast<const __nv_bfloat162*>(grow + d);
+        o0 *= __fdividef(1.f, 1.f + __expf(-__bfloat162float(g2.x)));
+        o1 *= __fdividef(1.f, 1.f + __expf(-__bfloat162float(g2.y)));
       }
       *reinterpret_cast<__nv_bfloat162*>(orow + d) = __floats2bfloat162_rn(o0, o1);
     }

@@ -40,6 +40,12 @@ template <int ACT> __device__ __forceinline__ float activate(float z) {
   return z;
 }
 
+// for activations that are rounded to bfloat16 right away: ex2.approx and a fast division
+template <int ACT> __device__ __forceinline__ float activate_fast(float z) {
+  if constexpr (ACT == ACT_SILU) return __fdividef(z, 1.f + __expf(-z));
+  return z;
+}
+
 template <typename T, int ACT>
 __global__ void __launch_bounds__(LA_COLS * (LA_MAX_DIM / LA_ROWS))
 linear_attention_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v, long long ld,
@@ -334,7 +340,7 @@ la_mma_sums_kernel(const bf16* __restrict__ k, const bf16* __restrict__ v, long 
       const float w = s < n ? pw[n - 1 - s] : 0.f;
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
-        const float kb = __bfloat162float(__float2bfloat16_rn(activate<ACT>(__bfloat162float(raw[b].v[i]))));
+        const float kb = __bfloat162float(__float2bfloat16_rn(activate_fast<ACT>(__bfloat162float(raw[b].v[i]))));
         split_bf16(kb * w, &kt_hi[(d + i) * LDT + s], &kt_lo[(d + i) * LDT + s]);
       }
     }
@@ -343,7 +349,7 @@ la_mma_sums_kernel(const bf16* __restrict__ k, const bf16* __restrict__ v, long 
   for (int i = 0; i < V_PER; ++i) {
     const int e = threadIdx.x + i * LM_WARPS * 32, s = e % LM_T, j = (e / LM_T) * 8;
 #pragma unroll
-    for (int x = 0; x < 8; ++x) vt[(j + x) * LDT + s] = __float2bfloat16_rn(activate<ACT>(__bfloat162float(rv[i].v[x])));
+    for (int x = 0; x < 8; ++x) vt[(j + x) * LDT + s] = __float2bfloat16_rn(activate_fast<ACT>(__bfloat162float(rv[i].v[x])));
   }
   __syncthreads();
   float* A = sums + (((long long)blockIdx.y * heads + head) * dim) * vdim;
@@ -437,8 +443,8 @@ la_mma_out_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, const 
       Pack8 oq, ok;
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
-        oq.v[i] = __float2bfloat16_rn(activate<ACT>(__bfloat162float(rq[b].v[i])));
-        ok.v[i] = __float2bfloat16_rn(activate<ACT>(__bfloat162float(rk[b].v[i])));
+        oq.v[i] = __float2bfloat16_rn(activate_fast<ACT>(__bfloat162float(rq[b].v[i])));
+        ok.v[i] = __float2bfloat16_rn(activate_fast<ACT>(__bfloat162float(rk[b].v[i])));
       }
       *reinterpret_cast<Pack8*>(qs + s * LDD + d) = oq;
       *reinterpret_cast<Pack8*>(ks_ + s * LDD + d) = ok;
@@ -467,7 +473,7 @@ la_mma_out_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, const 
   for (int i = 0; i < V_PER; ++i) {
     const int e = threadIdx.x + i * LM_WARPS * 32, s = e % LM_T, j = (e / LM_T) * 8;
 #pragma unroll
-    for (int x = 0; x < 8; ++x) vt[(j + x) * LDT + s] = __float2bfloat16_rn(activate<ACT>(__bfloat162float(rv[i].v[x])));
+    for (int x = 0; x < 8; ++x) vt[(j + x) * LDT + s] = __float2bfloat16_rn(activate_fast<ACT>(__bfloat162float(rv[i].v[x])));
   }
   for (int i = threadIdx.x; i <= LM_T; i += LM_WARPS * 32) pw[i] = powf(lam, (float)i);
   __syncthreads();
