@@ -93,3 +93,23 @@ def test_plain_implementation_is_causal_and_chunks_cut():
     alone = np.concatenate([plain.lightning_mixer(h[t:t + 1], Wl, "", m, 1e-5) for t in range(6)])
     assert np.allclose(whole, alone)
     assert np.allclose(plain.gelu_tanh(np.array([0.0, 10.0, -10.0])), [0.0, 10.0, 0.0], atol=1e-6)
+
+
+def test_command_line_creates_and_shows_a_model_folder(tmp_path, capsys):
+    import json
+    from hfee_b200 import cli
+    from hfee_b200.config import resolve_model_dir
+    from hfee_b200.parts.model import model_tensor_needs
+    from hfee_b200.weights import Checkpoint
+    cfg_path = tmp_path / "cfg.json"
+    cfg_path.write_text(json.dumps(du.DOB_B))
+    model = tmp_path / "model"
+    assert cli.main(["create", str(model), str(cfg_path), "--seed", "2"]) == 0
+    arch, cfg = resolve_model_dir(str(model))
+    assert arch.name == "Dobelix" and cfg.taps == 4
+    needs = model_tensor_needs(arch.build_spec(cfg))
+    Checkpoint(str(model)).check(needs)                 # everything asked for is there, nothing else
+    capsys.readouterr()
+    assert cli.main(["show", str(model)]) == 0
+    out = capsys.readouterr().out
+    assert "Dobelix" in out and f"{sum(int(np.prod(n.shape)) for n in needs.values()):,}" in out

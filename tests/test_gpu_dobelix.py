@@ -214,3 +214,22 @@ def test_greedy_generation_through_the_engine(models):
     eng = Engine(d, dtype="float32", page_size=16, max_context=128, max_requests=3, max_batch_tokens=48, prefill_chunk=11)
     got = [r.token_ids for r in eng.generate(prompts, SamplingOptions.greedy(num_predict=12))]
     assert got == want
+
+
+def test_command_line_generates(models):
+    """``bin/hfee-b200 run`` on a Dobelix folder: greedy tokens of the plain implementation, and a seeded draw
+    through the sampling chain that repeats."""
+    import os, subprocess, sys
+    d, cfg, seqs, _ = models["B"]
+    c, w = plain.load(d)
+    toks = [5, 6, 7]
+    for _ in range(6):
+        toks.append(int(np.argmax(plain.forward(c, w, toks)[-1])))
+    exe = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "bin", "hfee-b200")
+    base = [sys.executable, exe, "run", d, "--prompt-ids", "5,6,7", "--num-predict", "6", "--dtype", "float32", "--num-ctx", "256"]
+    p = subprocess.run(base + ["--temperature", "0", "--repeat-penalty", "1"], capture_output=True, text=True, timeout=300)
+    assert p.returncode == 0, p.stderr
+    assert p.stdout.split("\n")[0].split() == [str(t) for t in toks[3:]]
+    draws = [subprocess.run(base + ["--temperature", "0.9", "--top-k", "20", "--seed", "7"], capture_output=True, text=True,
+                            timeout=300).stdout.split("\n")[0] for _ in range(2)]
+    assert draws[0] == draws[1] and len(draws[0].split()) == 6
