@@ -233,38 +233,48 @@ qk_norm_rope_cache_kernel(const T* __restrict__ qk, long long ld_qk, const float
   const T* row = qk + (long long)i * ld_qk;
   const float2* csr = cs != nullptr ? cs + (long long)i * half : nullptr;
 
+  // a warp takes whole heads (no division per element; the key's page is looked up once per head)
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  constexpr int WARPS = ROW_THREADS / 32;
   float ss = 0.f;
   for (int c = threadIdx.x; c < q_cols; c += ROW_THREADS) { const float v = to_f32<T>(row[c]); ss = fmaf(v, v, ss); }
   const float q_scale = wq != nullptr ? 1.0f / sqrtf(block_sum(ss, partial) / (float)q_cols + eps) : 1.f;
-  for (int c = threadIdx.x; c < q_cols; c += ROW_THREADS) {
-    const int d = c % hd;
-    float val = to_f32<T>(row[c]) * q_scale * (wq != nullptr ? wq[c] : 1.f);
-    if (csr != nullptr && d < rope_dim) {
-      const int p = d < half ? c + half : c - half;                 // the dimension this one is paired with
-      const float other = to_f32<T>(row[p]) * q_scale * (wq != nullptr ? wq[p] : 1.f);
-      const float2 t = csr[d < half ? d : d - half];                // (cos, sin) of the pair's angle
-      val = d < half ? val * t.x - other * t.y : val * t.x + other * t.y;
+  for (int h = warp; h < heads; h += WARPS) {
+    const T* in = row + (long long)h * hd;
+    const float* wh = wq != nullptr ? wq + (long long)h * hd : nullptr;
+    T* dst = q_out + (long long)i * ld_q + (long long)h * hd;
+    for (int d = lane; d < hd; d += 32) {
+      float val = to_f32<T>(in[d]) * q_scale * (wh != nullptr ? wh[d] : 1.f);
+      if (csr != nullptr && d < rope_dim) {
+        const int p = d < half ? d + half : d - half;               // the dimension this one is paired with
+        const float other = to_f32<T>(in[p]) * q_scale * (wh != nullptr ? wh[p] : 1.f);
+        const float2 t = csr[d < half ? d : d - half];              // (cos, sin) of the pair's angle
+        val = d < half ? val * t.x - other * t.y : val * t.x + other * t.y;
+      }
+      dst[d] = from_f32<T>(val);
     }
-    q_out[(long long)i * ld_q + c] = from_f32<T>(val);
   }
   if (k_pool == nullptr) return;
   const T* krow = row + q_cols;
   ss = 0.f;
   for (int c = threadIdx.x; c < k_cols; c += ROW_THREADS) { const float v = to_f32<T>(krow[c]); ss = fmaf(v, v, ss); }
   const float k_scale = wk != nullptr ? 1.0f / sqrtf(block_sum(ss, partial) / (float)k_cols + eps) : 1.f;
-  for (int c = threadIdx.x; c < k_cols; c += ROW_THREADS) {
-    const int g = c / hd, d = c % hd;
-    const T raw = krow[c];
-    float val = to_f32<T>(raw) * k_scale * (wk != nullptr ? wk[c] : 1.f);
-    if (csr != nullptr && d < rope_dim) {
-      const int p = d < half ? c + half : c - half;
-      const float other = to_f32<T>(krow[p]) * k_scale * (wk != nullptr ? wk[p] : 1.f);
-      const float2 t = csr[d < half ? d : d - half];
-      val = d < half ? val * t.x - other * t.y : val * t.x + other * t.y;
+  for (int g = warp; g < cache.kv_heads; g += WARPS) {
+    const T* in = krow + (long long)g * hd;
+    const float* wh = wk != nullptr ? wk + (long long)g * hd : nullptr;
+    const long long at = paged_offset(cache, slot, pos, g);
+    for (int d = lane; d < hd; d += 32) {
+      const T raw = in[d];
+      float val = to_f32<T>(raw) * k_scale * (wh != nullptr ? wh[d] : 1.f);
+      if (csr != nullptr && d < rope_dim) {
+        const int p = d < half ? d + half : d - half;
+        const float other = to_f32<T>(in[p]) * k_scale * (wh != nullptr ? wh[p] : 1.f);
+        const float2 t = csr[d < half ? d : d - half];
+        val = d < half ? val * t.x - other * t.y : val * t.x + other * t.y;
+      }
+      k_pool[at + d] = from_f32<T>(val);
+      if (v_pool != nullptr) v_pool[at + d] = v_offset >= 0 ? row[v_offset + (long long)g * hd + d] : raw;
     }
-    const long long at = paged_offset(cache, slot, pos, g) + d;
-    k_pool[at] = from_f32<T>(val);
-    if (v_pool != nullptr) v_pool[at] = v_offset >= 0 ? row[v_offset + c] : raw;
   }
 }
 
