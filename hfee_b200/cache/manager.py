@@ -27,7 +27,8 @@ _TORCH = {"float32": torch.float32, "bfloat16": torch.bfloat16, "int32": torch.i
 @dataclass
 class CacheView:
     """What a mixer gets for one cache id: either pages (``k``, ``v`` of shape
-    [num_pages, kv_heads, page_size, head_dim], ``block_table`` int32
+    [num_pages, kv_heads, page_size, head_dim] (``v`` with the need's value size in place of head_dim, or None
+    when the need caches no values), ``block_table`` int32
     [max_requests, max_pages] on the device, ``page_size``) or ``state``
     ([max_requests, *shape], row = request slot); a layer that asked with a
     :class:`CacheBundle` gets its pages, if any, and ``states[name]`` for each named state."""
@@ -51,7 +52,8 @@ class _PagedGroup:
         self.dirty = True
         shape = (len(cache_ids), num_pages, need.kv_heads, page_size, need.head_dim)
         self.k = torch.zeros(shape, dtype=dtype, device=device)
-        self.v = torch.zeros(shape, dtype=dtype, device=device)
+        value_dim = need.head_dim if need.value_dim is None else int(need.value_dim)
+        self.v = torch.zeros(shape[:-1] + (value_dim,), dtype=dtype, device=device) if value_dim > 0 else None
         self.table_dev = torch.full((max_requests, max_pages), -1, dtype=torch.int32, device=device)
         # pinned staging copies of the table, used in turn, so that an upload never makes the host
         # wait for the GPU (a copy from pageable memory would)
@@ -112,7 +114,8 @@ class CacheManager:
                 self.paged.append(g)
                 for j, (cid, _) in enumerate(members):
                     view = self._views.setdefault(cid, CacheView())
-                    view.k, view.v, view.block_table, view.page_size = g.k[j], g.v[j], g.table_dev, page_size
+                    view.k, view.v = g.k[j], (g.v[j] if g.v is not None else None)
+                    view.block_table, view.page_size = g.table_dev, page_size
             else:
                 s = _StateGroup(need, ids, max_requests, self.device)
                 self.states.append(s)
@@ -231,7 +234,7 @@ class CacheManager:
         return min((g.pool.free_pages for g in self.paged), default=self.num_pages)
 
     def cache_bytes(self) -> int:
-        n = sum(g.k.numel() * g.k.element_size() * 2 for g in self.paged)
+        n = sum(t.numel() * t.element_size() for g in self.paged for t in (g.k, g.v) if t is not None)
         return n + sum(s.state.numel() * s.state.element_size() for s in self.states)
 
     def check_invariants(self) -> None:

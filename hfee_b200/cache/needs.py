@@ -9,11 +9,14 @@ from typing import Dict, Optional, Tuple
 class PagedKV:
     """Keys and values for every cached position (or, with ``window``, for the last
     ``window`` positions only; with ``chunk``, for the positions of the current block of
-    ``chunk`` positions counted from 0 only), stored in pages of ``page_size`` tokens."""
+    ``chunk`` positions counted from 0 only), stored in pages of ``page_size`` tokens.
+    ``value_dim``: size of a cached value; None = ``head_dim``; 0 = nothing is cached beside the keys (the
+    values are read out of the cached keys, as with a latent that serves as both)."""
     kv_heads: int
     head_dim: int
     window: Optional[int] = None
     chunk: Optional[int] = None
+    value_dim: Optional[int] = None
 
 
 @dataclass(frozen=True)

@@ -11,7 +11,10 @@
 // position lies in another block of `chunk` positions than the query's (blocks counted from
 // position 0 of the request); SIGMOID replaces the softmax by unnormalised weights
 // sigmoid(score * head_scale[h] + head_bias[h]) (either array may be missing); `gate` multiplies
-// the output element by element with sigmoid(gate[token, head * hd + d]).
+// the output element by element with sigmoid(gate[token, head * vd + d]), or, with GATE_PER_HEAD, every
+// element of head h with the one number sigmoid(gate[token, h]).  The values may have another size than the
+// keys (`vcache.head_dim`), and with v_pool == k_pool and a value size of at most the key size they are the
+// leading dimensions of the cached keys (a latent cache: one vector per token serves as key and as value).
 // Reference: hostfog/hfee internal/llm/forward.go:146-178 (scores scaled after the
 // dot, softmax over 0..pos, weighted sum of values), internal/ggml/ops.go:136-150.
 #include "common.cuh"
@@ -19,15 +22,19 @@
 namespace {
 
 constexpr int WARPS = 4;
-constexpr int MAX_HD = 256;
+constexpr int MAX_HD = 640;      // key size
+constexpr int MAX_VD = 512;      // value size
+constexpr int GATE_NONE = 0, GATE_ELEMENT = 1, GATE_PER_HEAD = 2;
 
 template <typename T, bool SIGMOID>
 __global__ void __launch_bounds__(WARPS * 32)
 attention_simt_kernel(const T* __restrict__ q, int ld_q, const T* __restrict__ k_pool,
-                      const T* __restrict__ v_pool, PagedCache cache, const int* __restrict__ positions,
+                      const T* __restrict__ v_pool, PagedCache cache, PagedCache vcache, int vd,
+                      const int* __restrict__ positions,
                       const int* __restrict__ slot_of_token, T* __restrict__ out, int ld_o, int n, int heads,
                       float scale, int window, int chunk, const float* __restrict__ head_scale,
-                      const float* __restrict__ head_bias, const T* __restrict__ gate, long long ld_gate) {
+                      const float* __restrict__ head_bias, const T* __restrict__ gate, long long ld_gate,
+                      int gate_mode) {
   pdl_wait();
   pdl_launch_dependents();
   __shared__ float q_s[WARPS][MAX_HD];
@@ -47,7 +54,7 @@ attention_simt_kernel(const T* __restrict__ q, int ld_q, const T* __restrict__ k
   for (int d = lane; d < hd; d += 32) q_s[warp][d] = to_f32<T>(qrow[d]);
   __syncwarp();
 
-  constexpr int DPL = MAX_HD / 32;     // output dims per lane
+  constexpr int DPL = MAX_VD / 32;     // output dims per lane
   float o[DPL];
 #pragma unroll
   for (int j = 0; j < DPL; ++j) o[j] = 0.f;
@@ -77,21 +84,22 @@ attention_simt_kernel(const T* __restrict__ q, int ld_q, const T* __restrict__ k
     int count = min(32, pos + 1 - base);
     for (int t = 0; t < count; ++t) {
       float pt = __shfl_sync(0xffffffffu, p, t);
-      const T* vr = v_pool + paged_offset(cache, slot, base + t, kvh);
+      const T* vr = v_pool + paged_offset(vcache, slot, base + t, kvh);
 #pragma unroll
       for (int j = 0; j < DPL; ++j) {
         int d = lane + 32 * j;
-        if (d < hd) o[j] = fmaf(pt, to_f32<T>(vr[d]), o[j]);
+        if (d < vd) o[j] = fmaf(pt, to_f32<T>(vr[d]), o[j]);
       }
     }
   }
-  T* orow = out + (long long)i * ld_o + (long long)h * hd;
+  T* orow = out + (long long)i * ld_o + (long long)h * vd;
   float inv = SIGMOID ? 1.f : 1.f / l;
-  const T* grow = gate != nullptr ? gate + (long long)i * ld_gate + (long long)h * hd : nullptr;
+  const T* grow = gate_mode == GATE_ELEMENT ? gate + (long long)i * ld_gate + (long long)h * vd : nullptr;
+  if (gate_mode == GATE_PER_HEAD) inv *= 1.f / (1.f + expf(-to_f32<T>(gate[(long long)i * ld_gate + h])));
 #pragma unroll
   for (int j = 0; j < DPL; ++j) {
     int d = lane + 32 * j;
-    if (d < hd) {
+    if (d < vd) {
       float v = o[j] * inv;
       if (grow != nullptr) v *= 1.f / (1.f + expf(-to_f32<T>(grow[d])));
       orow[d] = from_f32<T>(v);
@@ -103,49 +111,78 @@ attention_simt_kernel(const T* __restrict__ q, int ld_q, const T* __restrict__ k
 
 namespace {
 template <typename T>
-void launch_simt(const void* q, int ld_q, const void* k_pool, const void* v_pool, const PagedCache& c, const int* positions,
+void launch_simt(const void* q, int ld_q, const void* k_pool, const void* v_pool, const PagedCache& c, const PagedCache& vc,
+                 int vd, const int* positions,
                  const int* slot_of_token, void* out, int ld_o, int n, int heads, float scale, int window, int chunk,
                  int sigmoid, const float* head_scale, const float* head_bias, const void* gate, long long ld_gate,
-                 cudaStream_t stream) {
+                 int gate_mode, cudaStream_t stream) {
   long long tasks = (long long)n * heads;
   unsigned blocks = (unsigned)((tasks + WARPS - 1) / WARPS);
   if (sigmoid)
     hfee_launch(attention_simt_kernel<T, true>, dim3(blocks), dim3(WARPS * 32), 0, stream, (const T*)q, ld_q, (const T*)k_pool,
-                (const T*)v_pool, c, positions, slot_of_token, (T*)out, ld_o, n, heads, scale, window, chunk, head_scale,
-                head_bias, (const T*)gate, ld_gate);
+                (const T*)v_pool, c, vc, vd, positions, slot_of_token, (T*)out, ld_o, n, heads, scale, window, chunk, head_scale,
+                head_bias, (const T*)gate, ld_gate, gate_mode);
   else
     hfee_launch(attention_simt_kernel<T, false>, dim3(blocks), dim3(WARPS * 32), 0, stream, (const T*)q, ld_q, (const T*)k_pool,
-                (const T*)v_pool, c, positions, slot_of_token, (T*)out, ld_o, n, heads, scale, window, chunk, head_scale,
-                head_bias, (const T*)gate, ld_gate);
+                (const T*)v_pool, c, vc, vd, positions, slot_of_token, (T*)out, ld_o, n, heads, scale, window, chunk, head_scale,
+                head_bias, (const T*)gate, ld_gate, gate_mode);
 }
 }  // namespace
 
 // weights: 0 = softmax over the visible keys, 1 = sigmoid(score * head_scale[h] + head_bias[h]) per key.
+// value_dim: size of a value; v_pool is [pages][kv_heads][page_size][value_dim], or, with values_in_keys, the key
+// pool itself, whose leading value_dim dimensions are the values.  gate_mode: 0 none, 1 one number per output
+// element ([n, heads * value_dim]), 2 one number per head ([n, heads]); the output is multiplied by its sigmoid.
+HFEE_API int hfee_attention_simt_general(const void* q, int ld_q, const void* k_pool, const void* v_pool,
+                                         const int* block_table, int max_pages, int page_size, const int* positions,
+                                         const int* slot_of_token, void* out, int ld_o, int n, int heads, int kv_heads,
+                                         int head_dim, int value_dim, int values_in_keys, float scale, int window,
+                                         int chunk, int weights, const float* head_scale, const float* head_bias,
+                                         const void* gate, long long ld_gate, int gate_mode, int dtype,
+                                         cudaStream_t stream) {
+  if (n == 0) return HFEE_OK;
+  HFEE_REQUIRE(head_dim > 0 && head_dim <= MAX_HD, "attention_simt: head_dim %d is outside 1..%d", head_dim, MAX_HD);
+  HFEE_REQUIRE(value_dim > 0 && value_dim <= MAX_VD, "attention_simt: value_dim %d is outside 1..%d", value_dim, MAX_VD);
+  HFEE_REQUIRE(!values_in_keys || value_dim <= head_dim, "attention_simt: values inside keys need value_dim <= head_dim");
+  HFEE_REQUIRE(heads > 0 && kv_heads > 0 && heads % kv_heads == 0,
+               "attention_simt: heads %d must be a multiple of kv_heads %d", heads, kv_heads);
+  HFEE_REQUIRE(page_size > 0 && max_pages > 0, "attention_simt: bad cache sizes");
+  HFEE_REQUIRE(window >= 0 && chunk >= 0 && (weights == 0 || weights == 1), "attention_simt: bad mask or weight option");
+  HFEE_REQUIRE(gate_mode >= GATE_NONE && gate_mode <= GATE_PER_HEAD && (gate_mode == GATE_NONE) == (gate == nullptr),
+               "attention_simt: gate and gate_mode %d do not fit", gate_mode);
+  HFEE_REQUIRE(gate_mode != GATE_ELEMENT || ld_gate >= (long long)heads * value_dim, "attention_simt: ld_gate is too small");
+  HFEE_REQUIRE(gate_mode != GATE_PER_HEAD || ld_gate >= heads, "attention_simt: ld_gate is too small");
+  PagedCache c, vc;
+  HFEE_REQUIRE(make_paged_cache(&c, block_table, max_pages, page_size, kv_heads, head_dim),
+               "page_size %d must be a power of two", page_size);
+  if (values_in_keys) {
+    vc = c;
+    v_pool = k_pool;
+  } else {
+    make_paged_cache(&vc, block_table, max_pages, page_size, kv_heads, value_dim);
+  }
+  if (dtype == HFEE_F32)
+    launch_simt<float>(q, ld_q, k_pool, v_pool, c, vc, value_dim, positions, slot_of_token, out, ld_o, n, heads, scale,
+                       window, chunk, weights, head_scale, head_bias, gate, ld_gate, gate_mode, stream);
+  else if (dtype == HFEE_BF16)
+    launch_simt<__nv_bfloat16>(q, ld_q, k_pool, v_pool, c, vc, value_dim, positions, slot_of_token, out, ld_o, n, heads,
+                               scale, window, chunk, weights, head_scale, head_bias, gate, ld_gate, gate_mode, stream);
+  else
+    return hfee_fail(HFEE_ERR_ARG, "attention_simt: unknown dtype %d", dtype);
+  return hfee_check_launch("attention_simt");
+}
+
 HFEE_API int hfee_attention_simt_masked(const void* q, int ld_q, const void* k_pool, const void* v_pool,
                                         const int* block_table, int max_pages, int page_size, const int* positions,
                                         const int* slot_of_token, void* out, int ld_o, int n, int heads, int kv_heads,
                                         int head_dim, float scale, int window, int chunk, int weights,
                                         const float* head_scale, const float* head_bias, const void* gate,
                                         long long ld_gate, int dtype, cudaStream_t stream) {
-  if (n == 0) return HFEE_OK;
-  HFEE_REQUIRE(head_dim > 0 && head_dim <= MAX_HD, "attention_simt: head_dim %d is outside 1..%d", head_dim, MAX_HD);
-  HFEE_REQUIRE(heads > 0 && kv_heads > 0 && heads % kv_heads == 0,
-               "attention_simt: heads %d must be a multiple of kv_heads %d", heads, kv_heads);
-  HFEE_REQUIRE(page_size > 0 && max_pages > 0, "attention_simt: bad cache sizes");
-  HFEE_REQUIRE(window >= 0 && chunk >= 0 && (weights == 0 || weights == 1), "attention_simt: bad mask or weight option");
-  HFEE_REQUIRE(gate == nullptr || ld_gate >= (long long)heads * head_dim, "attention_simt: ld_gate is too small");
-  PagedCache c;
-  HFEE_REQUIRE(make_paged_cache(&c, block_table, max_pages, page_size, kv_heads, head_dim),
-               "page_size %d must be a power of two", page_size);
-  if (dtype == HFEE_F32)
-    launch_simt<float>(q, ld_q, k_pool, v_pool, c, positions, slot_of_token, out, ld_o, n, heads, scale, window, chunk,
-                       weights, head_scale, head_bias, gate, ld_gate, stream);
-  else if (dtype == HFEE_BF16)
-    launch_simt<__nv_bfloat16>(q, ld_q, k_pool, v_pool, c, positions, slot_of_token, out, ld_o, n, heads, scale, window,
-                               chunk, weights, head_scale, head_bias, gate, ld_gate, stream);
-  else
-    return hfee_fail(HFEE_ERR_ARG, "attention_simt: unknown dtype %d", dtype);
-  return hfee_check_launch("attention_simt");
+  HFEE_REQUIRE(head_dim > 0 && head_dim <= MAX_VD, "attention_simt: head_dim %d is outside 1..%d", head_dim, MAX_VD);
+  return hfee_attention_simt_general(q, ld_q, k_pool, v_pool, block_table, max_pages, page_size, positions, slot_of_token,
+                                     out, ld_o, n, heads, kv_heads, head_dim, head_dim, 0, scale, window, chunk, weights,
+                                     head_scale, head_bias, gate, ld_gate, gate != nullptr ? GATE_ELEMENT : GATE_NONE,
+                                     dtype, stream);
 }
 
 HFEE_API int hfee_attention_simt(const void* q, int ld_q, const void* k_pool, const void* v_pool,

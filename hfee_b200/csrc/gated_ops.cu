@@ -399,3 +399,115 @@ HFEE_API int hfee_qk_norm_rope_cache(const void* qk, long long ld_qk, const floa
     return hfee_fail(HFEE_ERR_ARG, "qk_norm_rope_cache: unknown dtype %d", dtype);
   return hfee_check_launch("qk_norm_rope_cache");
 }
+
+// ---------------------------------------------------------------------------------------------------------------
+//   hfee_head_norm_gate   per (token, head): out = x / sqrt(mean_head(x^2) + eps) * w[d] * act(gate), the weight
+//                         [head_dim] shared by the heads; act = sigmoid or SiLU
+//   hfee_unary_act        out = act(x) element by element; act = relu(x)^2
+//   hfee_head_gate        x[i, h, :] *= sigmoid(gate[i, h]): one gate number per head
+namespace {
+
+constexpr int HG_SIGMOID = 0, HG_SILU = 1;
+constexpr int UA_RELU2 = 0;
+
+template <typename T>
+__global__ void __launch_bounds__(128)
+head_norm_gate_kernel(const float* __restrict__ x, long long ld_x, const float* __restrict__ w, float eps,
+                      const T* __restrict__ gate, long long ld_g, T* __restrict__ out, long long ld_o, int n, int heads,
+                      int head_dim, int act) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int lane = threadIdx.x & 31;
+  const long long task = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (task >= (long long)n * heads) return;
+  const int i = (int)(task / heads), h = (int)(task % heads);
+  const float* xr = x + (long long)i * ld_x + (long long)h * head_dim;
+  const T* gr = gate + (long long)i * ld_g + (long long)h * head_dim;
+  T* orow = out + (long long)i * ld_o + (long long)h * head_dim;
+  float ss = 0.f;
+  for (int d = lane; d < head_dim; d += 32) ss = fmaf(xr[d], xr[d], ss);
+  const float scale = 1.0f / sqrtf(warp_sum(ss) / (float)head_dim + eps);
+  for (int d = lane; d < head_dim; d += 32) {
+    const float g = to_f32<T>(gr[d]);
+    const float s = sigmoid_f32(g);
+    orow[d] = from_f32<T>(xr[d] * scale * w[d] * (act == HG_SILU ? g * s : s));
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+unary_act_kernel(const T* __restrict__ x, long long ld_x, T* __restrict__ out, long long ld_o, int cols, long long total, int act) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const long long e = (long long)blockIdx.x * 256 + threadIdx.x;
+  if (e >= total) return;
+  const long long r = e / cols;
+  const int c = (int)(e - r * cols);
+  const float v = fmaxf(to_f32<T>(x[r * ld_x + c]), 0.f);
+  out[r * ld_o + c] = from_f32<T>(v * v);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+head_gate_kernel(T* __restrict__ x, long long ld_x, const T* __restrict__ gate, long long ld_g, int heads, int head_dim,
+                 long long total) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const long long e = (long long)blockIdx.x * 256 + threadIdx.x;
+  if (e >= total) return;
+  const int cols = heads * head_dim;
+  const long long r = e / cols;
+  const int c = (int)(e - r * cols);
+  const float g = sigmoid_f32(to_f32<T>(gate[r * ld_g + c / head_dim]));
+  x[r * ld_x + c] = from_f32<T>(to_f32<T>(x[r * ld_x + c]) * g);
+}
+
+}  // namespace
+
+HFEE_API int hfee_head_norm_gate(const float* x, long long ld_x, const float* w, float eps, const void* gate, long long ld_g,
+                                 void* out, long long ld_o, int n, int heads, int head_dim, int act, int dtype,
+                                 cudaStream_t stream) {
+  if (n == 0) return HFEE_OK;
+  const long long width = (long long)heads * head_dim;
+  HFEE_REQUIRE(n > 0 && heads > 0 && head_dim > 0 && ld_x >= width && ld_g >= width && ld_o >= width, "head_norm_gate: bad sizes");
+  HFEE_REQUIRE(act == HG_SIGMOID || act == HG_SILU, "head_norm_gate: unknown gate activation %d", act);
+  const unsigned blocks = (unsigned)(((long long)n * heads + 3) / 4);
+  if (dtype == HFEE_F32)
+    hfee_launch(head_norm_gate_kernel<float>, dim3(blocks), dim3(128), 0, stream, x, ld_x, w, eps, (const float*)gate, ld_g, (float*)out, ld_o, n, heads, head_dim, act);
+  else if (dtype == HFEE_BF16)
+    hfee_launch(head_norm_gate_kernel<__nv_bfloat16>, dim3(blocks), dim3(128), 0, stream, x, ld_x, w, eps, (const __nv_bfloat16*)gate, ld_g, (__nv_bfloat16*)out, ld_o, n, heads, head_dim, act);
+  else
+    return hfee_fail(HFEE_ERR_ARG, "head_norm_gate: unknown dtype %d", dtype);
+  return hfee_check_launch("head_norm_gate");
+}
+
+HFEE_API int hfee_unary_act(const void* x, long long ld_x, void* out, long long ld_o, int rows, int cols, int act, int dtype,
+                            cudaStream_t stream) {
+  if (rows == 0 || cols == 0) return HFEE_OK;
+  HFEE_REQUIRE(rows > 0 && cols > 0 && ld_x >= cols && ld_o >= cols, "unary_act: bad sizes");
+  HFEE_REQUIRE(act == UA_RELU2, "unary_act: unknown activation %d", act);
+  const long long total = (long long)rows * cols;
+  const unsigned blocks = (unsigned)((total + 255) / 256);
+  if (dtype == HFEE_F32)
+    hfee_launch(unary_act_kernel<float>, dim3(blocks), dim3(256), 0, stream, (const float*)x, ld_x, (float*)out, ld_o, cols, total, act);
+  else if (dtype == HFEE_BF16)
+    hfee_launch(unary_act_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, (const __nv_bfloat16*)x, ld_x, (__nv_bfloat16*)out, ld_o, cols, total, act);
+  else
+    return hfee_fail(HFEE_ERR_ARG, "unary_act: unknown dtype %d", dtype);
+  return hfee_check_launch("unary_act");
+}
+
+HFEE_API int hfee_head_gate(void* x, long long ld_x, const void* gate, long long ld_g, int n, int heads, int head_dim, int dtype,
+                            cudaStream_t stream) {
+  if (n == 0) return HFEE_OK;
+  HFEE_REQUIRE(n > 0 && heads > 0 && head_dim > 0 && ld_x >= (long long)heads * head_dim && ld_g >= heads, "head_gate: bad sizes");
+  const long long total = (long long)n * heads * head_dim;
+  const unsigned blocks = (unsigned)((total + 255) / 256);
+  if (dtype == HFEE_F32)
+    hfee_launch(head_gate_kernel<float>, dim3(blocks), dim3(256), 0, stream, (float*)x, ld_x, (const float*)gate, ld_g, heads, head_dim, total);
+  else if (dtype == HFEE_BF16)
+    hfee_launch(head_gate_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, (__nv_bfloat16*)x, ld_x, (const __nv_bfloat16*)gate, ld_g, heads, head_dim, total);
+  else
+    return hfee_fail(HFEE_ERR_ARG, "head_gate: unknown dtype %d", dtype);
+  return hfee_check_launch("head_gate");
+}

@@ -1,0 +1,218 @@
+// What sits between an attention's input projection and its score kernel, for layouts the fused
+// q/k/v epilogues do not cover.  Float32 arithmetic, one rounding on the way out.
+//
+//   hfee_rope_norm_cache        per head: rotate `rope_dim` dimensions that start anywhere in the head
+//                               (dimension i with i + rope_dim/2), then optionally divide the head by its
+//                               root mean square (no weight); queries to a buffer whose head stride and
+//                               offset may differ from the source's, keys into their cache page at an
+//                               offset within the cached vector, values copied to theirs.  Key and value
+//                               sizes are independent.
+//   hfee_latent_norm_rope_cache one token's down-projections of a latent attention: the query latent
+//                               RMS-normed with its weight into a buffer, the key/value latent RMS-normed
+//                               with its weight into the leading dimensions of the token's cached vector,
+//                               the rotated tail behind it.
+#include "common.cuh"
+
+namespace {
+
+constexpr int RN_WARPS = 4;
+constexpr int RN_MAX_LEN = 640;
+constexpr int RN_PER_LANE = RN_MAX_LEN / 32;
+
+struct HeadGroup {
+  int count;          // heads of this kind
+  int src_off;        // column of head 0 in the source row
+  int src_stride;     // columns from one head to the next
+  int len;            // dimensions taken per head
+  int rope_off;       // first rotated dimension within the head (ignored without a table)
+  int dst_off;        // where the head's dimensions start in the destination vector
+  int dst_stride;     // query buffer: columns from one head to the next; pools: unused
+};
+
+// x[d] of a head after rotation; the partner dimension is read from the source as well
+template <typename T>
+__device__ __forceinline__ float rotated(const T* __restrict__ x, int d, int rope_off, int rope_dim,
+                                         const float* __restrict__ cs) {
+  const float v = to_f32<T>(x[d]);
+  const int half = rope_dim >> 1, r = d - rope_off;
+  if (cs == nullptr || r < 0 || r >= rope_dim) return v;
+  if (r < half) return v * cs[2 * r] - to_f32<T>(x[d + half]) * cs[2 * r + 1];
+  const int i = r - half;
+  return v * cs[2 * i] + to_f32<T>(x[d - half]) * cs[2 * i + 1];
+}
+
+template <typename T>
+__global__ void __launch_bounds__(RN_WARPS * 32)
+rope_norm_cache_kernel(const T* __restrict__ src, long long ld_src, int n, const float* __restrict__ cs, int rope_dim,
+                       float norm_eps, const int* __restrict__ positions, const int* __restrict__ slot_of_token,
+                       HeadGroup qg, T* __restrict__ q_out, long long ld_q, HeadGroup kg, T* __restrict__ k_pool,
+                       PagedCache kc, HeadGroup vg, T* __restrict__ v_pool, PagedCache vc) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int per_token = qg.count + kg.count + vg.count;
+  const long long task = (long long)blockIdx.x * RN_WARPS + warp;
+  if (task >= (long long)n * per_token) return;
+  const int i = (int)(task / per_token);
+  int h = (int)(task % per_token);
+  const T* row = src + (long long)i * ld_src;
+  const float* csr = cs != nullptr ? cs + (long long)i * rope_dim : nullptr;
+  HeadGroup g;
+  T* dst;
+  bool norm = norm_eps >= 0.f;
+  if (h < qg.count) {
+    g = qg;
+    dst = q_out + (long long)i * ld_q + (long long)h * g.dst_stride + g.dst_off;
+  } else if (h < qg.count + kg.count) {
+    h -= qg.count;
+    g = kg;
+    dst = k_pool + paged_offset(kc, slot_of_token[i], positions[i], h) + g.dst_off;
+  } else {
+    h -= qg.count + kg.count;
+    g = vg;
+    dst = v_pool + paged_offset(vc, slot_of_token[i], positions[i], h) + g.dst_off;
+    norm = false;
+    csr = nullptr;
+  }
+  const T* x = row + g.src_off + (long long)h * g.src_stride;
+  float v[RN_PER_LANE];
+  float ss = 0.f;
+#pragma unroll
+  for (int j = 0; j < RN_PER_LANE; ++j) {
+    const int d = lane + 32 * j;
+    v[j] = d < g.len ? rotated<T>(x, d, g.rope_off, rope_dim, csr) : 0.f;
+    ss = fmaf(v[j], v[j], ss);
+  }
+  float scale = 1.f;
+  if (norm) scale = 1.0f / sqrtf(warp_sum(ss) / (float)g.len + norm_eps);
+#pragma unroll
+  for (int j = 0; j < RN_PER_LANE; ++j) {
+    const int d = lane + 32 * j;
+    if (d < g.len) dst[d] = from_f32<T>(v[j] * scale);
+  }
+}
+
+constexpr int LT_THREADS = 128;
+
+__device__ __forceinline__ float block_sum_lt(float v, float* partial) {
+  v = warp_sum(v);
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) partial[threadIdx.x >> 5] = v;
+  __syncthreads();
+  float total = 0.f;
+#pragma unroll
+  for (int i = 0; i < LT_THREADS / 32; ++i) total += partial[i];
+  return total;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(LT_THREADS)
+latent_norm_rope_cache_kernel(const T* __restrict__ proj, long long ld, int q_off, int q_rank, int kv_off, int kv_rank,
+                              int rot_dim, const float* __restrict__ wq, const float* __restrict__ wkv, float eps,
+                              const float* __restrict__ cs, const int* __restrict__ positions,
+                              const int* __restrict__ slot_of_token, T* __restrict__ cq_out, long long ld_cq,
+                              T* __restrict__ k_pool, PagedCache kc, int write_cache) {
+  __shared__ float partial[LT_THREADS / 32];
+  pdl_wait();
+  pdl_launch_dependents();
+  const int i = blockIdx.x;
+  const T* row = proj + (long long)i * ld;
+  {
+    const T* x = row + q_off;
+    float ss = 0.f;
+    for (int d = threadIdx.x; d < q_rank; d += LT_THREADS) { const float v = to_f32<T>(x[d]); ss = fmaf(v, v, ss); }
+    const float scale = 1.0f / sqrtf(block_sum_lt(ss, partial) / (float)q_rank + eps);
+    T* dst = cq_out + (long long)i * ld_cq;
+    for (int d = threadIdx.x; d < q_rank; d += LT_THREADS) dst[d] = from_f32<T>(to_f32<T>(x[d]) * scale * wq[d]);
+  }
+  if (!write_cache) return;
+  {
+    const T* x = row + kv_off;
+    float ss = 0.f;
+    for (int d = threadIdx.x; d < kv_rank; d += LT_THREADS) { const float v = to_f32<T>(x[d]); ss = fmaf(v, v, ss); }
+    const float scale = 1.0f / sqrtf(block_sum_lt(ss, partial) / (float)kv_rank + eps);
+    T* dst = k_pool + paged_offset(kc, slot_of_token[i], positions[i], 0);
+    for (int d = threadIdx.x; d < kv_rank; d += LT_THREADS) dst[d] = from_f32<T>(to_f32<T>(x[d]) * scale * wkv[d]);
+    const float* csr = cs + (long long)i * rot_dim;
+    for (int d = threadIdx.x; d < rot_dim; d += LT_THREADS)
+      dst[kv_rank + d] = from_f32<T>(rotated<T>(x + kv_rank, d, 0, rot_dim, csr));
+  }
+}
+
+template <typename T>
+int launch_rope_norm(const void* src, long long ld_src, int n, const float* cs, int rope_dim, float norm_eps,
+                     const int* positions, const int* slot_of_token, const HeadGroup& qg, void* q_out, long long ld_q,
+                     const HeadGroup& kg, void* k_pool, const PagedCache& kc, const HeadGroup& vg, void* v_pool,
+                     const PagedCache& vc, cudaStream_t stream) {
+  const long long tasks = (long long)n * (qg.count + kg.count + vg.count);
+  if (tasks == 0) return HFEE_OK;
+  const unsigned blocks = (unsigned)((tasks + RN_WARPS - 1) / RN_WARPS);
+  hfee_launch(rope_norm_cache_kernel<T>, dim3(blocks), dim3(RN_WARPS * 32), 0, stream, (const T*)src, ld_src, n, cs, rope_dim,
+              norm_eps, positions, slot_of_token, qg, (T*)q_out, ld_q, kg, (T*)k_pool, kc, vg, (T*)v_pool, vc);
+  return hfee_check_launch("rope_norm_cache");
+}
+
+}  // namespace
+
+// q_out, k_pool and v_pool may each be null: that kind of head is then skipped.  norm_eps < 0: no norm.
+// cs: [n, rope_dim / 2, 2] cosines and sines of the step's tokens, or null for no rotation.
+HFEE_API int hfee_rope_norm_cache(const void* src, long long ld_src, int dtype, int n, const float* cs, int rope_dim,
+                                  float norm_eps, const int* positions, const int* slot_of_token,
+                                  int heads, int q_src_off, int q_src_stride, int q_len, int q_rope_off, void* q_out,
+                                  long long ld_q, int q_dst_off, int q_dst_stride,
+                                  int kv_heads, int k_src_off, int k_src_stride, int k_len, int k_rope_off, void* k_pool,
+                                  int k_pool_dim, int k_dst_off,
+                                  int v_src_off, int v_src_stride, int v_len, void* v_pool, int v_pool_dim,
+                                  const int* block_table, int max_pages, int page_size, cudaStream_t stream) {
+  if (n == 0) return HFEE_OK;
+  HFEE_REQUIRE(q_len <= RN_MAX_LEN && k_len <= RN_MAX_LEN && v_len <= RN_MAX_LEN, "rope_norm_cache: a head is longer than %d",
+               RN_MAX_LEN);
+  HFEE_REQUIRE(rope_dim >= 0 && rope_dim % 2 == 0, "rope_norm_cache: rope_dim %d must be even", rope_dim);
+  HeadGroup qg{q_out != nullptr ? heads : 0, q_src_off, q_src_stride, q_len, q_rope_off, q_dst_off, q_dst_stride};
+  HeadGroup kg{k_pool != nullptr ? kv_heads : 0, k_src_off, k_src_stride, k_len, k_rope_off, k_dst_off, 0};
+  HeadGroup vg{v_pool != nullptr ? kv_heads : 0, v_src_off, v_src_stride, v_len, 0, 0, 0};
+  if (cs != nullptr) {
+    HFEE_REQUIRE(qg.count == 0 || (q_rope_off >= 0 && q_rope_off + rope_dim <= q_len), "rope_norm_cache: rotated query dimensions leave the head");
+    HFEE_REQUIRE(kg.count == 0 || (k_rope_off >= 0 && k_rope_off + rope_dim <= k_len), "rope_norm_cache: rotated key dimensions leave the head");
+  }
+  PagedCache kc{}, vc{};
+  if (kg.count) {
+    HFEE_REQUIRE(k_dst_off + k_len <= k_pool_dim, "rope_norm_cache: key does not fit its cached vector");
+    HFEE_REQUIRE(make_paged_cache(&kc, block_table, max_pages, page_size, kv_heads, k_pool_dim), "page_size %d must be a power of two", page_size);
+  }
+  if (vg.count) {
+    HFEE_REQUIRE(v_len <= v_pool_dim, "rope_norm_cache: value does not fit its cached vector");
+    HFEE_REQUIRE(make_paged_cache(&vc, block_table, max_pages, page_size, kv_heads, v_pool_dim), "page_size %d must be a power of two", page_size);
+  }
+  if (dtype == HFEE_F32)
+    return launch_rope_norm<float>(src, ld_src, n, cs, rope_dim, norm_eps, positions, slot_of_token, qg, q_out, ld_q, kg, k_pool, kc, vg, v_pool, vc, stream);
+  if (dtype == HFEE_BF16)
+    return launch_rope_norm<__nv_bfloat16>(src, ld_src, n, cs, rope_dim, norm_eps, positions, slot_of_token, qg, q_out, ld_q, kg, k_pool, kc, vg, v_pool, vc, stream);
+  return hfee_fail(HFEE_ERR_ARG, "rope_norm_cache: unknown dtype %d", dtype);
+}
+
+// proj rows hold the query latent at q_off (q_rank columns) and [key/value latent | tail to rotate] at kv_off
+// (kv_rank + rot_dim columns).  The cached vector of a token is [normed latent | rotated tail] (one "head").
+HFEE_API int hfee_latent_norm_rope_cache(const void* proj, long long ld, int dtype, int n, int q_off, int q_rank, int kv_off,
+                                         int kv_rank, int rot_dim, const float* wq, const float* wkv, float eps,
+                                         const float* cs, const int* positions, const int* slot_of_token, void* cq_out,
+                                         long long ld_cq, void* k_pool, const int* block_table, int max_pages,
+                                         int page_size, cudaStream_t stream) {
+  if (n == 0) return HFEE_OK;
+  HFEE_REQUIRE(q_rank > 0 && kv_rank > 0 && rot_dim > 0 && rot_dim % 2 == 0, "latent_norm_rope_cache: bad sizes");
+  HFEE_REQUIRE(cs != nullptr || k_pool == nullptr, "latent_norm_rope_cache: the rotated tail needs its table");
+  PagedCache kc{};
+  if (k_pool != nullptr)
+    HFEE_REQUIRE(make_paged_cache(&kc, block_table, max_pages, page_size, 1, kv_rank + rot_dim), "page_size %d must be a power of two", page_size);
+  if (dtype == HFEE_F32)
+    hfee_launch(latent_norm_rope_cache_kernel<float>, dim3(n), dim3(LT_THREADS), 0, stream, (const float*)proj, ld, q_off, q_rank,
+                kv_off, kv_rank, rot_dim, wq, wkv, eps, cs, positions, slot_of_token, (float*)cq_out, ld_cq, (float*)k_pool, kc,
+                k_pool != nullptr ? 1 : 0);
+  else if (dtype == HFEE_BF16)
+    hfee_launch(latent_norm_rope_cache_kernel<__nv_bfloat16>, dim3(n), dim3(LT_THREADS), 0, stream, (const __nv_bfloat16*)proj, ld,
+                q_off, q_rank, kv_off, kv_rank, rot_dim, wq, wkv, eps, cs, positions, slot_of_token, (__nv_bfloat16*)cq_out, ld_cq,
+                (__nv_bfloat16*)k_pool, kc, k_pool != nullptr ? 1 : 0);
+  else
+    return hfee_fail(HFEE_ERR_ARG, "latent_norm_rope_cache: unknown dtype %d", dtype);
+  return hfee_check_launch("latent_norm_rope_cache");
+}

@@ -61,6 +61,17 @@ _SIGNATURES = {
     "hfee_scale_f32": [_P, _L, _I, _I, _F, _P],
     "hfee_cast_rows": [_P, _P, _L, _I, _I, _I, _P],
     "hfee_qk_norm_rope_cache": [_P, _L, _P, _P, _F, _P, _I, _P, _P, _P, _L, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P],
+    "hfee_attention_simt_general": [_P, _I, _P, _P, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I, _I, _I, _P, _P, _P, _L, _I, _I, _P],
+    "hfee_rope_norm_cache": [_P, _L, _I, _I, _P, _I, _F, _P, _P, _I, _I, _I, _I, _I, _P, _L, _I, _I, _I, _I, _I, _I, _I, _P, _I, _I,
+                             _I, _I, _I, _P, _I, _P, _I, _I, _P],
+    "hfee_latent_norm_rope_cache": [_P, _L, _I, _I, _I, _I, _I, _I, _I, _P, _P, _F, _P, _P, _P, _P, _L, _P, _P, _I, _I, _P],
+    "hfee_head_linear": [_P, _L, _I, _I, _P, _P, _L, _I, _I, _I, _I, _I, _I, _P, _L, _I, _P],
+    "hfee_conv_act": [_P, _L, _I, _P, _P, _P, _P, _P, _L, _I, _I, _I, _I, _I, _I, _P],
+    "hfee_conv_act_launches": [_I, _I, _I],
+    "hfee_delta_rule": [_P, _L, _I, _I, _I, _P, _L, _I, _I, _I, _P, _P, _P, _P, _P, _P, _L, _I, _I, _I, _I, _I, _I, _P],
+    "hfee_head_norm_gate": [_P, _L, _P, _F, _P, _L, _P, _L, _I, _I, _I, _I, _I, _P],
+    "hfee_unary_act": [_P, _L, _P, _L, _I, _I, _I, _I, _P],
+    "hfee_head_gate": [_P, _L, _P, _L, _I, _I, _I, _I, _P],
     "hfee_sample": [_P, _L, _I, _I, _P, _P, _P, _L, _P, _P, _P, _P],
     "hfee_argmax": [_P, _L, _I, _I, _I, _P, _P, _P, _P, _P],
     "hfee_sample_chain": [_P, _L, _I, _I, _P, _P, _P, _I, _P, _I, _P, _L, _P, _P, _P],
@@ -933,6 +944,197 @@ def sigmoid_attention(q, k_pool, v_pool, block_table, page_size, step, out, head
                           kv_heads, head_dim, scale, window, chunk, WEIGHTS_SIGMOID, head_scale, head_bias, gate)
 
 
+# ---------------------------------------------------------------------------- independent key and value sizes, latents, the delta rule
+GATE_NONE, GATE_ELEMENT, GATE_PER_HEAD = 0, 1, 2
+HEAD_GATE_ACTIVATIONS = {"sigmoid": 0, "silu": 1}
+UNARY_ACTIVATIONS = {"relu2": 0}
+
+
+def attention_simt_general(q, k_pool, v_pool, block_table, page_size, positions, slot_of_token, out, heads, kv_heads,
+                           head_dim, value_dim, scale, window=0, chunk=0, gate=None, gate_mode=GATE_NONE) -> None:
+    """Softmax attention over the paged cache on the CUDA cores in float32 arithmetic with a value size of its
+    own: ``v_pool`` is [pages, kv_heads, page_size, value_dim], or None when the values are the leading
+    ``value_dim`` dimensions of the cached keys.  ``gate`` multiplies the output by its sigmoid: one number per
+    output element (GATE_ELEMENT, [n, heads * value_dim]) or per head (GATE_PER_HEAD, [n, heads])."""
+    lib = library()
+    _i32(positions, "positions"); _i32(slot_of_token, "slot_of_token"); _i32(block_table, "block_table")
+    n = q.shape[0]
+    assert q.shape[1] == heads * head_dim and tuple(out.shape) == (n, heads * value_dim) and q.dtype == k_pool.dtype == out.dtype
+    assert k_pool.is_contiguous() and tuple(k_pool.shape[1:]) == (kv_heads, page_size, head_dim)
+    if v_pool is not None:
+        assert v_pool.is_contiguous() and v_pool.dtype == q.dtype and tuple(v_pool.shape[1:]) == (kv_heads, page_size, value_dim)
+    assert (gate is None) == (gate_mode == GATE_NONE) and (gate is None or gate.dtype == q.dtype)
+    _check(lib.hfee_attention_simt_general(q.data_ptr(), _rows(q, "q"), k_pool.data_ptr(), _ptr(v_pool), block_table.data_ptr(),
+                                           block_table.shape[1], page_size, positions.data_ptr(), slot_of_token.data_ptr(),
+                                           out.data_ptr(), _rows(out, "attention out"), n, heads, kv_heads, head_dim,
+                                           value_dim, int(v_pool is None), float(scale), int(window or 0), int(chunk or 0),
+                                           WEIGHTS_SOFTMAX, None, None, _ptr(gate),
+                                           _rows(gate, "gate") if gate is not None else 0, int(gate_mode), _dt(q), _stream()), lib)
+
+
+# The grouped-query kernels on the tensor cores take bfloat16 queries and keys and round the softmax weights to
+# bfloat16 for the product with the values; the CUDA-core kernel keeps scores and weights in float32.
+GATED_ATTENTION_ON_TENSOR_CORES = True
+
+
+def softmax_attention_on_tensor_cores(q: torch.Tensor, out: torch.Tensor, heads: int, kv_heads: int, head_dim: int,
+                                      value_dim: int, page_size: int, step) -> bool:
+    """True when :func:`paged_attention` runs this step on the tensor cores: bfloat16, values of the keys' size,
+    and sizes those kernels are built for."""
+    group = heads // kv_heads
+    if not (GATED_ATTENTION_ON_TENSOR_CORES and q.dtype == torch.bfloat16 and head_dim == value_dim and step is not None
+            and head_dim % 16 == 0 and 16 <= head_dim <= 256 and group <= 64 and _rows(q, "q") % 8 == 0):
+        return False
+    return True
+
+
+def latent_attention(q: torch.Tensor, k_pool: torch.Tensor, block_table: torch.Tensor, page_size: int, step,
+                     out: torch.Tensor, heads: int, cached_dim: int, value_dim: int, scale: float, window: int = 0) -> None:
+    """Softmax attention of ``heads`` query heads over ONE cached vector per token (``k_pool`` [pages, 1, page_size,
+    cached_dim]) whose leading ``value_dim`` dimensions are also the values: ``out`` [n, heads * value_dim]."""
+    attention_simt_general(q, k_pool, None, block_table, page_size, step.positions, step.slot_of_token, out, heads, 1,
+                           cached_dim, value_dim, scale, window)
+
+
+def linear_act(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, activation: str) -> None:
+    """out = act(a @ w.T) for an activation of :data:`UNARY_ACTIVATIONS`."""
+    linear(a, w, out)
+    unary_act(out, out, activation)
+
+
+def rope_norm_cache(src: torch.Tensor, cs: Optional[torch.Tensor], rope_dim: int, norm_eps: Optional[float],
+                    positions: torch.Tensor, slot_of_token: torch.Tensor, block_table: torch.Tensor, page_size: int,
+                    q=None, k=None, v=None) -> None:
+    """Per head of a row of ``src``: rotate ``rope_dim`` dimensions (dimension i with i + rope_dim/2) by the step's
+    (cos, sin) table ``cs``, then divide the head by its root mean square (``norm_eps`` None: no norm), and store.
+    ``q`` = (heads, src_off, src_stride, len, rope_off, out, dst_off, dst_stride): queries into the buffer ``out``;
+    ``k`` = (kv_heads, src_off, src_stride, len, rope_off, pool, dst_off): keys into their cache page at ``dst_off``
+    within the cached vector; ``v`` = (src_off, src_stride, len, pool): values copied as they are.  Any may be None."""
+    lib = library()
+    _i32(positions, "positions"); _i32(slot_of_token, "slot_of_token"); _i32(block_table, "block_table")
+    n = src.shape[0]
+    assert cs is None or (cs.dtype == torch.float32 and cs.is_contiguous() and cs.numel() == n * rope_dim)
+    qh, qso, qss, ql, qro, qout, qdo, qds = q if q is not None else (0, 0, 0, 0, 0, None, 0, 0)
+    kh, kso, kss, kl, kro, kpool, kdo = k if k is not None else (0, 0, 0, 0, 0, None, 0)
+    vso, vss, vl, vpool = v if v is not None else (0, 0, 0, None)
+    for t in (qout, kpool, vpool):
+        assert t is None or t.dtype == src.dtype
+    assert kpool is None or (kpool.is_contiguous() and kpool.shape[1] == kh and kpool.shape[2] == page_size)
+    assert vpool is None or (vpool.is_contiguous() and kpool is not None and vpool.shape[1] == kh and vpool.shape[2] == page_size)
+    _check(lib.hfee_rope_norm_cache(src.data_ptr(), _rows(src, "src"), _dt(src), n, _ptr(cs), int(rope_dim) if cs is not None else 0,
+                                    -1.0 if norm_eps is None else float(norm_eps), positions.data_ptr(), slot_of_token.data_ptr(),
+                                    qh, qso, qss, ql, qro, _ptr(qout), _rows(qout, "q out") if qout is not None else 0, qdo, qds,
+                                    kh, kso, kss, kl, kro, _ptr(kpool), kpool.shape[3] if kpool is not None else 0, kdo,
+                                    vso, vss, vl, _ptr(vpool), vpool.shape[3] if vpool is not None else 0,
+                                    block_table.data_ptr(), block_table.shape[1], page_size, _stream()), lib)
+
+
+def latent_norm_rope_cache(proj: torch.Tensor, q_off: int, q_rank: int, kv_off: int, kv_rank: int, rot_dim: int,
+                           q_weight: torch.Tensor, kv_weight: torch.Tensor, eps: float, cs: torch.Tensor,
+                           positions: torch.Tensor, slot_of_token: torch.Tensor, cq_out: torch.Tensor,
+                           k_pool: Optional[torch.Tensor], block_table: torch.Tensor, page_size: int) -> None:
+    """The down-projections of a latent attention, per token: ``proj[:, q_off : q_off + q_rank]`` RMS-normed with
+    ``q_weight`` into ``cq_out``; ``proj[:, kv_off : kv_off + kv_rank]`` RMS-normed with ``kv_weight`` into the leading
+    dimensions of the token's cached vector and the ``rot_dim`` columns behind it, rotated, into the rest
+    (``k_pool`` [pages, 1, page_size, kv_rank + rot_dim]; None: only the query latent)."""
+    lib = library()
+    _i32(positions, "positions"); _i32(slot_of_token, "slot_of_token"); _i32(block_table, "block_table")
+    n = proj.shape[0]
+    assert q_weight.dtype == kv_weight.dtype == torch.float32 and q_weight.numel() == q_rank and kv_weight.numel() == kv_rank
+    assert cs.dtype == torch.float32 and cs.is_contiguous() and cs.numel() == n * rot_dim and cq_out.dtype == proj.dtype
+    if k_pool is not None:
+        assert k_pool.dtype == proj.dtype and k_pool.is_contiguous() and tuple(k_pool.shape[1:]) == (1, page_size, kv_rank + rot_dim)
+    _check(lib.hfee_latent_norm_rope_cache(proj.data_ptr(), _rows(proj, "proj"), _dt(proj), n, q_off, q_rank, kv_off, kv_rank,
+                                           rot_dim, q_weight.data_ptr(), kv_weight.data_ptr(), float(eps), cs.data_ptr(),
+                                           positions.data_ptr(), slot_of_token.data_ptr(), cq_out.data_ptr(),
+                                           _rows(cq_out, "cq_out"), _ptr(k_pool), block_table.data_ptr(), block_table.shape[1],
+                                           page_size, _stream()), lib)
+
+
+def head_linear(x: torch.Tensor, in_off: int, in_stride: int, w: torch.Tensor, out: torch.Tensor, out_off: int,
+                out_stride: int, gate: Optional[torch.Tensor] = None) -> None:
+    """out[i, out_off + h * out_stride + o] = sum_k w[h, o, k] * x[i, in_off + h * in_stride + k], times
+    sigmoid(gate[i, h]) if ``gate`` [n, heads] is given.  ``w`` is [heads, n_out, n_in]."""
+    lib = library()
+    heads, n_out, n_in = w.shape
+    n = x.shape[0]
+    assert w.is_contiguous() and x.dtype == w.dtype == out.dtype and out.shape[0] == n
+    assert in_off + (heads - 1) * in_stride + n_in <= x.shape[1] and out_off + (heads - 1) * out_stride + n_out <= out.shape[1]
+    assert gate is None or (gate.dtype == x.dtype and gate.shape == (n, heads))
+    _check(lib.hfee_head_linear(x.data_ptr(), _rows(x, "x"), in_off, in_stride, w.data_ptr(), out.data_ptr(), _rows(out, "out"),
+                                out_off, out_stride, n, heads, n_in, n_out, _ptr(gate),
+                                _rows(gate, "gate") if gate is not None else 0, _dt(x), _stream()), lib)
+
+
+def conv_act(x: torch.Tensor, weight: torch.Tensor, state: torch.Tensor, step, out: torch.Tensor, activation: str = "silu",
+             write_state: bool = True) -> None:
+    """out[t, c] = act(sum_j weight[c, j] * x[t - taps + 1 + j, c]) per request of the step, inputs in front of the
+    step's tokens taken from ``state`` [slots, taps - 1, width] (float32), which then takes the request's last
+    taps - 1 inputs.  ``x`` and ``out`` are [n, width] views (any row stride) of the activations' dtype."""
+    lib = library()
+    n, width = x.shape
+    taps = weight.shape[1]
+    assert weight.dtype == torch.float32 and weight.is_contiguous() and weight.shape[0] == width
+    assert state.dtype == torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == (taps - 1, width)
+    assert out.shape == x.shape and out.dtype == x.dtype
+    _check(lib.hfee_conv_act(x.data_ptr(), _rows(x, "conv in"), _dt(x), weight.data_ptr(), state.data_ptr(),
+                             step.cu_tokens.data_ptr(), step.slots.data_ptr(), out.data_ptr(), _rows(out, "conv out"), step.r,
+                             step.max_new, width, taps, ACTIVATIONS[activation], int(write_state), _stream()), lib)
+    if lib.hfee_conv_act_launches(step.max_new, taps, int(write_state)) > 1:
+        count_launches(1)
+
+
+def delta_rule(qkv: torch.Tensor, q_off: int, k_off: int, v_off: int, ba: torch.Tensor, b_off: int, a_off: int,
+               a_log: torch.Tensor, dt_bias: torch.Tensor, state: torch.Tensor, step, out: torch.Tensor, heads: int,
+               qk_heads: int, dim: int, vdim: int, write_state: bool = True) -> None:
+    """The gated delta rule over the step's tokens, continuing each request's float32 state ``state``
+    [slots, heads, dim, vdim]: S <- g S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q, with q and k made unit
+    vectors per head first (q also times dim^-1/2), beta = sigmoid(b) and g = exp(-exp(a_log) softplus(a + dt_bias)).
+    ``qkv`` rows hold the queries and keys of ``qk_heads`` heads and the values of ``heads`` heads at the given
+    column offsets, ``ba`` rows one b and one a per head.  ``out`` is float32 [n, heads * vdim]."""
+    lib = library()
+    n = qkv.shape[0]
+    assert qkv.dtype == ba.dtype and ba.shape[0] == n and out.dtype == torch.float32 and tuple(out.shape) == (n, heads * vdim)
+    assert a_log.dtype == dt_bias.dtype == torch.float32 and a_log.numel() == dt_bias.numel() == heads
+    assert state.dtype == torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == (heads, dim, vdim)
+    assert max(q_off, k_off) + qk_heads * dim <= qkv.shape[1] and v_off + heads * vdim <= qkv.shape[1]
+    assert max(b_off, a_off) + heads <= ba.shape[1]
+    _check(lib.hfee_delta_rule(qkv.data_ptr(), _rows(qkv, "qkv"), q_off, k_off, v_off, ba.data_ptr(), _rows(ba, "ba"), b_off,
+                               a_off, _dt(qkv), a_log.data_ptr(), dt_bias.data_ptr(), state.data_ptr(),
+                               step.cu_tokens.data_ptr(), step.slots.data_ptr(), out.data_ptr(), _rows(out, "out"), step.r,
+                               heads, qk_heads, dim, vdim, int(write_state), _stream()), lib)
+
+
+def head_norm_gate(x: torch.Tensor, weight: torch.Tensor, eps: float, gate: torch.Tensor, out: torch.Tensor, heads: int,
+                   head_dim: int, activation: str = "sigmoid") -> None:
+    """Per (row, head): out = x / sqrt(mean over the head of x^2 + eps) * weight[d] * act(gate), ``weight`` [head_dim]
+    shared by the heads, ``act`` sigmoid or SiLU.  ``x`` is float32; ``gate`` and ``out`` share a dtype."""
+    lib = library()
+    n = x.shape[0]
+    assert x.dtype == torch.float32 and gate.dtype == out.dtype and tuple(gate.shape) == tuple(x.shape) == tuple(out.shape) == (n, heads * head_dim)
+    assert weight.dtype == torch.float32 and weight.numel() == head_dim
+    _check(lib.hfee_head_norm_gate(x.data_ptr(), _rows(x, "x"), weight.data_ptr(), float(eps), gate.data_ptr(), _rows(gate, "gate"),
+                                   out.data_ptr(), _rows(out, "out"), n, heads, head_dim, HEAD_GATE_ACTIVATIONS[activation],
+                                   _dt(out), _stream()), lib)
+
+
+def unary_act(x: torch.Tensor, out: torch.Tensor, activation: str) -> None:
+    """out = act(x) element by element; ``activation``: ``"relu2"`` (the square of relu).  ``out`` may be ``x``."""
+    lib = library()
+    assert x.shape == out.shape and x.dtype == out.dtype and x.dim() == 2
+    _check(lib.hfee_unary_act(x.data_ptr(), _rows(x, "x"), out.data_ptr(), _rows(out, "out"), x.shape[0], x.shape[1],
+                              UNARY_ACTIVATIONS[activation], _dt(x), _stream()), lib)
+
+
+def head_gate(x: torch.Tensor, gate: torch.Tensor, heads: int, head_dim: int) -> None:
+    """x[i, h * head_dim + d] *= sigmoid(gate[i, h]) in place."""
+    lib = library()
+    n = x.shape[0]
+    assert x.shape[1] == heads * head_dim and gate.dtype == x.dtype and tuple(gate.shape) == (n, heads)
+    _check(lib.hfee_head_gate(x.data_ptr(), _rows(x, "x"), gate.data_ptr(), _rows(gate, "gate"), n, heads, head_dim, _dt(x),
+                              _stream()), lib)
+
+
 def rmsnorm_add(y: torch.Tensor, weight: torch.Tensor, residual: torch.Tensor, eps: float, add_unit: bool = False,
                 cast_out: Optional[torch.Tensor] = None) -> None:
     """residual += y * rsqrt(mean(y^2) + eps) * weight, all float32.  With ``cast_out`` the new residual rows
@@ -1090,7 +1292,8 @@ def argmax(logits: torch.Tensor, out: torch.Tensor, scratch: torch.Tensor, slots
 
 
 # the entry points the parts and the sampler launch through can be left out by class (see tag())
-for _name in ("attention_simt_masked", "short_conv", "linear_attention", "rmsnorm_add", "norm_gate", "gated_act", "scale_", "cast_rows", "sigmoid_attention",
+for _name in ("attention_simt_general", "rope_norm_cache", "latent_norm_rope_cache", "head_linear", "conv_act", "delta_rule",
+              "head_norm_gate", "unary_act", "head_gate", "attention_simt_masked", "short_conv", "linear_attention", "rmsnorm_add", "norm_gate", "gated_act", "scale_", "cast_rows", "sigmoid_attention",
               "qk_norm_rope_cache", "embed", "rmsnorm", "rope_table", "rope_cache_write", "swiglu", "linear", "linear_normed", "linear_swiglu", "linear_rope_cache",
               "linear_swiglu_normed", "paged_attention", "paged_attention_rope", "sample", "argmax", "sample_chain"):
     globals()[_name] = _measurable(globals()[_name])

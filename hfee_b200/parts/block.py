@@ -106,5 +106,37 @@ class OutputNormBlock(Block):
             part.forward(x, y, step, *cache_args)
 
 
+class SandwichNormBlock(Block):
+    """``x += norm_out(mixer(norm_in(x))); x += norm_out'(feed_forward(norm_in'(x)))``: a norm in front of every
+    sublayer and another on its output.  ``ffn`` with ``ffn_norm`` and ``ffn_out_norm`` is optional (a layer may have
+    no feed-forward).  The layer's cache is whatever the mixer asks for."""
+    needs = ("mixer", "mixer_norm", "mixer_out_norm")
+    graph_safe = True
+
+    def __init__(self, spec, tensors, rt, parts):
+        super().__init__(spec, tensors, rt, parts)
+        self.mixer, self.mixer_norm, self.mixer_out_norm = parts["mixer"], parts["mixer_norm"], parts["mixer_out_norm"]
+        self.feed_forward = parts.get("ffn")
+        self.ffn_norm, self.ffn_out_norm = parts.get("ffn_norm"), parts.get("ffn_out_norm")
+        if (self.feed_forward is None) != (self.ffn_norm is None) or (self.feed_forward is None) != (self.ffn_out_norm is None):
+            raise ValueError("a feed-forward comes with its input norm and its output norm")
+        self.width = int(spec.width)
+
+    def forward(self, residual: torch.Tensor, step: Any, cache: Any, writes_cache: bool) -> None:
+        rt, n = self.rt, step.n
+        xn = rt.scratch("block_normed", (rt.max_tokens, self.width))[:n]
+        y = rt.scratch("block_sublayer_out", (rt.max_tokens, self.width), torch.float32)[:n]
+        self.mixer_norm.forward(residual, xn)
+        OutputNormBlock._run(self.mixer, y, xn, step, cache, writes_cache)
+        if self.feed_forward is None:
+            self.mixer_out_norm.forward_add(y, residual)
+            return
+        # the output norm's kernel also leaves the next sublayer's normed input
+        self.mixer_out_norm.forward_add(y, residual, then=self.ffn_norm, then_out=xn)
+        OutputNormBlock._run(self.feed_forward, y, xn, step)
+        self.ffn_out_norm.forward_add(y, residual)
+
+
+register_part("block", "sandwich_norm", SandwichNormBlock)
 register_part("block", "pre_norm", PreNormBlock)
 register_part("block", "output_norm", OutputNormBlock)

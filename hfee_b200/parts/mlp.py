@@ -58,5 +58,35 @@ class SwiGLUFeedForward(Part):
         ops.linear(h, self.w_down, residual, accumulate=accumulate)
 
 
+class DenseFeedForward(Part):
+    """``down(act(up(x)))`` without a gate.  spec: ``width``, ``inner``, ``activation`` (``"relu2"``: the square of
+    relu).  ``forward(..., accumulate=False)`` stores the output instead of adding it."""
+    can_overwrite = True
+    category = "feed_forward"
+    graph_safe = True
+
+    @staticmethod
+    def tensor_needs(spec: PartSpec) -> Dict[str, TensorNeed]:
+        return {"up": TensorNeed((spec.inner, spec.width)), "down": TensorNeed((spec.width, spec.inner))}
+
+    def __init__(self, spec, tensors, rt):
+        super().__init__(spec, tensors, rt)
+        self.inner = int(spec.inner)
+        self.activation = str(spec.activation)
+        if self.activation not in ops.UNARY_ACTIVATIONS:
+            raise ValueError(f"unknown feed-forward activation {self.activation!r} (known: {sorted(ops.UNARY_ACTIVATIONS)})")
+        self.w_up, self.w_down = tensors["up"], tensors["down"]
+
+    def forward(self, xn: torch.Tensor, residual: torch.Tensor, step: Any, accumulate: bool = True) -> None:
+        n, rt = step.n, self.rt
+        xn = xn if isinstance(xn, torch.Tensor) else xn.tensor()
+        h = rt.scratch("ffn_hidden", (rt.max_tokens, self.inner))[:n]
+        ops.tag("up")
+        ops.linear_act(xn, self.w_up, h, self.activation)
+        ops.tag("down")
+        ops.linear(h, self.w_down, residual, accumulate=accumulate)
+
+
+register_part("feed_forward", "dense", DenseFeedForward)
 register_part("feed_forward", "swiglu", SwiGLUFeedForward)
 register_part("feed_forward", "gated", SwiGLUFeedForward)       # the same part named for its general form

@@ -34,11 +34,15 @@ class RMSNorm(Part):
         ops.tag(before)
 
 
-    def forward_add(self, y: torch.Tensor, residual: torch.Tensor, cast_out: Optional[torch.Tensor] = None) -> None:
+    def forward_add(self, y: torch.Tensor, residual: torch.Tensor, cast_out: Optional[torch.Tensor] = None,
+                    then: Optional["RMSNorm"] = None, then_out: Optional[torch.Tensor] = None) -> None:
         """``residual += norm(y)``: the norm on a sublayer's output (both float32); ``cast_out`` also takes
-        the new residual in the dtype the next matrix product reads."""
+        the new residual in the dtype the next matrix product reads.  With ``then`` (another norm) the new
+        residual, normed by it, goes to ``then_out``: the input of the sublayer that follows."""
         before = ops.tag("norm")
         ops.rmsnorm_add(y, self.weight, residual, self.eps, add_unit=self.add_unit, cast_out=cast_out)
+        if then is not None:
+            ops.rmsnorm(residual, then.weight, then_out, then.eps, add_unit=then.add_unit)
         ops.tag(before)
 
     def fused_params(self):
