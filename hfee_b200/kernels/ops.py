@@ -65,6 +65,8 @@ _SIGNATURES = {
     "hfee_rope_norm_cache": [_P, _L, _I, _I, _P, _I, _F, _P, _P, _I, _I, _I, _I, _I, _P, _L, _I, _I, _I, _I, _I, _I, _I, _P, _I, _I,
                              _I, _I, _I, _P, _I, _P, _I, _I, _P],
     "hfee_latent_norm_rope_cache": [_P, _L, _I, _I, _I, _I, _I, _I, _I, _P, _P, _F, _P, _P, _P, _P, _L, _P, _P, _I, _I, _P],
+    "hfee_latent_attention_mma": [_P, _L, _P, _P, _I, _I, _P, _P, _P, _P, _L, _I, _I, _I, _I, _I, _F, _I, _P],
+    "hfee_latent_attention_mma_supports": [_I, _I, _I],
     "hfee_head_linear": [_P, _L, _I, _I, _P, _P, _L, _I, _I, _I, _I, _I, _I, _P, _L, _I, _P],
     "hfee_conv_act": [_P, _L, _I, _P, _P, _P, _P, _P, _L, _I, _I, _I, _I, _I, _I, _P],
     "hfee_conv_act_launches": [_I, _I, _I],
@@ -991,9 +993,37 @@ def softmax_attention_on_tensor_cores(q: torch.Tensor, out: torch.Tensor, heads:
 def latent_attention(q: torch.Tensor, k_pool: torch.Tensor, block_table: torch.Tensor, page_size: int, step,
                      out: torch.Tensor, heads: int, cached_dim: int, value_dim: int, scale: float, window: int = 0) -> None:
     """Softmax attention of ``heads`` query heads over ONE cached vector per token (``k_pool`` [pages, 1, page_size,
-    cached_dim]) whose leading ``value_dim`` dimensions are also the values: ``out`` [n, heads * value_dim]."""
+    cached_dim]) whose leading ``value_dim`` dimensions are also the values: ``out`` [n, heads * value_dim].
+    bfloat16 with sizes the tensor-core kernel takes runs there (prompt portions and decode steps alike),
+    everything else on the CUDA cores in float32."""
+    if (USE_LATENT_MMA and q.dtype == torch.bfloat16 and latent_mma_supports(heads, cached_dim, value_dim)
+            and _rows(q, "q") % 8 == 0 and q.data_ptr() % 16 == 0 and _rows(out, "out") % 2 == 0 and out.data_ptr() % 4 == 0):
+        lib = library()
+        for t, what in ((block_table, "block_table"), (step.cu_tokens, "cu_tokens"), (step.slots, "slots"),
+                        (step.context_before, "context_before")):
+            _i32(t, what)
+        assert k_pool.dtype == out.dtype == torch.bfloat16 and k_pool.is_contiguous()
+        assert tuple(k_pool.shape[1:]) == (1, page_size, cached_dim)
+        assert tuple(q.shape) == (step.n, heads * cached_dim) and tuple(out.shape) == (step.n, heads * value_dim)
+        _check(lib.hfee_latent_attention_mma(q.data_ptr(), _rows(q, "q"), k_pool.data_ptr(), block_table.data_ptr(),
+                                             block_table.shape[1], page_size, step.cu_tokens.data_ptr(), step.slots.data_ptr(),
+                                             step.context_before.data_ptr(), out.data_ptr(), _rows(out, "out"), step.r,
+                                             step.max_new, heads, cached_dim, value_dim, float(scale), int(window or 0),
+                                             _stream()), lib)
+        return
     attention_simt_general(q, k_pool, None, block_table, page_size, step.positions, step.slot_of_token, out, heads, 1,
                            cached_dim, value_dim, scale, window)
+
+
+USE_LATENT_MMA = True
+_LATENT_MMA_TAKES: dict = {}
+
+
+def latent_mma_supports(heads: int, cached_dim: int, value_dim: int) -> bool:
+    key = (heads, cached_dim, value_dim)
+    if key not in _LATENT_MMA_TAKES:
+        _LATENT_MMA_TAKES[key] = bool(library().hfee_latent_attention_mma_supports(*key))
+    return _LATENT_MMA_TAKES[key]
 
 
 def linear_act(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, activation: str) -> None:
@@ -1292,7 +1322,7 @@ def argmax(logits: torch.Tensor, out: torch.Tensor, scratch: torch.Tensor, slots
 
 
 # the entry points the parts and the sampler launch through can be left out by class (see tag())
-for _name in ("attention_simt_general", "rope_norm_cache", "latent_norm_rope_cache", "head_linear", "conv_act", "delta_rule",
+for _name in ("latent_attention", "linear_act", "attention_simt_general", "rope_norm_cache", "latent_norm_rope_cache", "head_linear", "conv_act", "delta_rule",
               "head_norm_gate", "unary_act", "head_gate", "attention_simt_masked", "short_conv", "linear_attention", "rmsnorm_add", "norm_gate", "gated_act", "scale_", "cast_rows", "sigmoid_attention",
               "qk_norm_rope_cache", "embed", "rmsnorm", "rope_table", "rope_cache_write", "swiglu", "linear", "linear_normed", "linear_swiglu", "linear_rope_cache",
               "linear_swiglu_normed", "paged_attention", "paged_attention_rope", "sample", "argmax", "sample_chain"):

@@ -76,6 +76,8 @@ ALONE = {
     "delta_wide_keys": bu.delta(1, 1, 144, 40, 3),
     "latent": bu.latent(4, 16, 8, 16, 24, 32, window=9, base=100.0, scale=0.5),
     "latent_one_head_no_window": bu.latent(1, 8, 24, 40, 72, 8, window=None, base=1.0e4, scale=0.3),
+    "latent_tensor_core_sizes": bu.latent(5, 24, 16, 40, 56, 32, window=21, base=300.0, scale=0.4),
+    "latent_many_heads_wide_values": bu.latent(34, 8, 16, 8, 16, 80, window=None, base=50.0, scale=0.3),
     "attention_gqa_small_values": bu.attention(4, 1, 16, 8, 8, 100.0, 0.5),
     "attention_odd_sizes_window": bu.attention(3, 3, 24, 40, 24, 10.0, 0.3, scaling=(2.0, 1.0, 8.0, 16), window=7),
     "attention_tensor_core_sizes": bu.attention(4, 2, 64, 64, 48, 1.0e4, 0.2),
@@ -121,7 +123,7 @@ def test_window_and_page_edges(tmp_path, dtype, kind):
     window, the first tokens (which see fewer keys than a window), for prompt portions that start at, before and
     after an edge and for single decoded tokens.  A large score scale makes single keys dominate."""
     window, page = 24, 16
-    make = (lambda wd: bu.latent(2, 16, 8, 16, 16, 16, window=wd, base=30.0, scale=2.5)) if kind == "latent" else \
+    make = (lambda wd: bu.latent(2, 16, 16, 16, 16, 16, window=wd, base=30.0, scale=2.5)) if kind == "latent" else \
            (lambda wd: bu.attention(2, 1, 16, 16, 16, 30.0, 1.2, window=wd))
     cfg = bu.config(32, 60, [make(window)])
     d = bu.write_model(str(tmp_path), cfg, seed=21)
@@ -149,12 +151,17 @@ def _far_check(d, dtype, first=1):
     c, w = plain.load(d)
     seq, other = _far_sequences(first)
     ref, ref_other = plain.forward(c, w, seq), plain.forward(c, w, other)
-    assert ru.rel_err(ref_other[-8:], ref[-8:]) > 5 * TOL[dtype]         # the far token matters
+    effect = ru.rel_err(ref_other[-8:], ref[-8:])
+    assert effect > 5 * TOL[dtype]                                       # the far token matters
+    # float32: rounding of sums.  bfloat16: every logit here hangs on a handful of rounded numbers (one layer, weights
+    # made so that one key or a few writes decide), so the largest difference is held to a tenth of what the far
+    # token changes, and the root mean square to the usual bound.
+    limit = TOL[dtype] if dtype == "float32" else max(TOL[dtype], effect / 10)
     runner = bu.make_runner(d, dtype, 416, page_size=32, max_requests=1)
     for s, r in ((other, ref_other), (seq, ref)):                        # the same slot and pages twice
         steps = ru.portions([s], sizes=(130, 2, 67, 1, 1, 100, 64)) if s is seq else ru.prefill_then_decode([s], tail=40)
         got = ru.run_in_process(runner, steps)
-        assert ru.rel_err(got[0], r) < TOL[dtype]
+        assert ru.rel_err(got[0], r) < limit and rms_err(got[0], r) < RMS_TOL[dtype]
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
