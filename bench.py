@@ -18,7 +18,9 @@ than the 126 MB L2, so no L2 flush is needed between steps.
 layers, named beside the full number in ``config``), ``--dtype float32`` the true 32-bit path.
 ``--design dobelix`` prints, instead of the line above, prompt and decode times of a Dobelix model (linear
 attention with decay, chunked sigmoid attention, short convolutions, norms on the sublayers' outputs) beside a
-Llama model of the same width, heads, feed-forward and number of layers, with what each class of kernels costs.
+Llama model of the same width, heads, feed-forward and number of layers, with what each class of kernels costs;
+``--design bamipel`` the same for a Bamipel model (gated delta rule, latent attention under a sliding window, gated
+grouped-query attention, norms on both sides of every sublayer, a relu^2 feed-forward).
 ``--breakdown`` prints, instead of the line above, what each class of kernels costs inside the decode
 step at batch 1, 8 and 64 and inside the prompt pass: the step is timed again with that class's
 launches left out (results wrong, timing not), and the difference is the class's cost in place.
@@ -170,8 +172,46 @@ def dobelix_like(model, layers, chunk=128):
             "norm": {"eps": 1e-5}, "canon": {"taps": 4}, "embedding": {"scale": 1.0}, "logit_scale": 1.0}
 
 
+def bamipel_like(model, layers, window=512):
+    """A Bamipel configuration of the layer sizes of the Llama configuration ``model``: in turn the gated delta rule
+    (as many value heads, a query/key head per key/value head), latent attention (a key/value latent of four head
+    sizes, a rotated part of half a head, a query latent of three eighths of the width, a sliding window) and gated
+    grouped-query attention."""
+    h, kv, hd = model["num_attention_heads"], model["num_key_value_heads"], model["head_dim"]
+    ff = {"kind": "dense", "ff": model["intermediate_size"]}
+    width = model["hidden_size"]
+    out = []
+    for i in range(layers):
+        if i % 3 == 0:
+            out.append({"type": "delta", "mlp": ff, "mixer": {"heads": h, "kv_heads": kv, "dim": hd, "vdim": hd, "conv": 4}})
+        elif i % 3 == 1:
+            out.append({"type": "latent_attention", "mlp": ff,
+                        "mixer": {"heads": h, "dim": hd, "rot_dim": hd // 2, "vdim": hd, "q_rank": 3 * width // 8,
+                                  "kv_rank": 4 * hd, "mask": {"size": window}, "rot": {"dims": hd // 2, "base": 10000.0},
+                                  "scale": (hd + hd // 2) ** -0.5}})
+        else:
+            out.append({"type": "attention", "mlp": ff,
+                        "mixer": {"heads": h, "kv_heads": kv, "dim": hd, "vdim": hd, "scale": 1.0 / hd,
+                                  "rot": {"dims": hd, "base": 500000.0,
+                                          "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}})
+    return {"architecture": "Bamipel", "vocab": model["vocab_size"], "width": width, "layers": out, "norm": {"eps": 1e-5}}
+
+
+DESIGNS = {"dobelix": dobelix_like, "bamipel": bamipel_like}
+# kernel classes (the names the parts tag their launches with) that only some layers of a design have: class -> the layer
+# types that have it; every other class is counted once per layer ("head": once per model)
+DESIGN_CLASSES = {
+    "dobelix": {"conv": ("lightning", "attention"), "gate": ("lightning",), "linear_attention": ("lightning",),
+                "rope": ("attention",), "attention": ("attention",)},
+    "bamipel": {"conv": ("delta",), "delta_rule": ("delta",), "gate": ("delta",), "rope": ("attention", "latent_attention"),
+                "attention": ("attention", "latent_attention"), "fold": ("latent_attention",), "expand": ("latent_attention",)},
+}
+CLASS_ORDER = ("conv", "norm", "qkv", "rope", "fold", "attention", "expand", "linear_attention", "delta_rule", "gate", "o",
+               "gate_up", "up", "down", "head")
+
+
 def design_comparison(args):
-    """Prompt pass and decode step of a Dobelix model and of the Llama model of equal layer sizes, and the cost
+    """Prompt pass and decode step of a model of the named design and of the Llama model of equal layer sizes, and the cost
     of each class of kernels inside them (step time minus step time with the class's launches left out)."""
     import shutil
     import numpy as np
@@ -184,7 +224,7 @@ def design_comparison(args):
     layers = args.layers or 6
     base = dict(base, num_hidden_layers=layers, vocab_size=32768, tie_word_embeddings=True,
                 max_position_embeddings=max(base["max_position_embeddings"], 2 * args.prompt))
-    designs = {"llama": base, "dobelix": dobelix_like(base, layers)}
+    designs = {"llama": base, args.design: DESIGNS[args.design](base, layers)}
     rng = np.random.default_rng(0)
     out = {"design_comparison": f"{base_name} layer sizes, {layers} layers, vocabulary 32768, bf16, random weights",
            "prompt_tokens": args.prompt, "decode_batch": args.batch,
@@ -239,14 +279,18 @@ def design_comparison(args):
             runner._graphs.clear()
             runner._graph_seen.clear()
 
-        kinds = [l["type"] for l in cfg["layers"]] if name == "dobelix" else ["attention"] * layers
-        having = {"conv": layers if name == "dobelix" else 0, "gate": kinds.count("lightning") if name == "dobelix" else 0,
-                  "linear_attention": kinds.count("lightning") if name == "dobelix" else 0,
-                  "rope": kinds.count("attention"), "attention": kinds.count("attention")}
+        if name == "llama":
+            having = {"rope": layers, "attention": layers, "gate_up": layers, "up": 0}
+            having.update({c: 0 for c in ("conv", "gate", "linear_attention", "delta_rule", "fold", "expand")})
+        else:
+            kinds = [l["type"] for l in cfg["layers"]]
+            having = {c: sum(kinds.count(k) for k in types) for c, types in DESIGN_CLASSES[name].items()}
+            having.update({c: 0 for cs in DESIGN_CLASSES.values() for c in cs if c not in having})
+            having.update({"gate_up": layers, "up": 0} if name == "dobelix" else {"gate_up": 0, "up": layers})
 
         def classes_of(measure, rounds=3):
             res = {}
-            for c in ("conv", "norm", "qkv", "rope", "attention", "linear_attention", "gate", "o", "gate_up", "down", "head"):
+            for c in CLASS_ORDER:
                 n = having.get(c, 1 if c == "head" else layers)
                 if n == 0:
                     continue
@@ -306,7 +350,7 @@ def main():
     ap.add_argument("--prompt", type=int, default=PROMPT,
                     help="tokens of the prompts (other context lengths than the headline's 2,048; the cache holds twice as many per request)")
     ap.add_argument("--no-graphs", action="store_true", help="profiling aid: launch decode kernels one by one")
-    ap.add_argument("--design", default=None, choices=["dobelix"],
+    ap.add_argument("--design", default=None, choices=sorted(DESIGNS),
                     help="instead of the bench line: this design beside the Llama model of equal layer sizes "
                          "(--shape, --layers, --prompt, --batch apply; --no-points skips the cost per class of kernels)")
     args = ap.parse_args()

@@ -9,10 +9,10 @@
 //                     q and k are first made unit vectors (x / sqrt(sum x^2 + 1e-6); q also times dim^-1/2),
 //                     beta_t = sigmoid(b_t), g_t = exp(-exp(A_log) * softplus(a_t + dt_bias)), all float32.
 //                     Columns of S evolve independently: S[:, j] <- g S[:, j] + k * beta (v_j - g S[:, j].k), so a
-//                     block owns DR_COLS columns of one (request, head), DR_LANES lanes share a column (each keeps
-//                     dim / DR_LANES of its entries in registers), and the tokens of the step are walked in order:
-//                     the result does not depend on how a prompt was cut.  Tiles of DR_TILE tokens are staged in
-//                     shared memory (normalised there) between two barriers.
+//                     block owns DR_COLS columns of one (request, head), a warp one column (each lane keeps dim / 32
+//                     of its entries in registers), and the tokens of the step are taken in tiles of DR_TILE, each
+//                     solved at once (see the kernel): the result depends on how a prompt was cut only through the
+//                     order of float32 sums.
 #include "common.cuh"
 
 namespace {
@@ -92,18 +92,10 @@ int launch_conv_act(const void* x, long long ld_x, const float* w, float* state,
 }
 
 // ---------------------------------------------------------------------------------------------------------------
-constexpr int DR_LANES = 8;                  // lanes that share a column of the state
-constexpr int DR_THREADS = 128;
-constexpr int DR_COLS = DR_THREADS / DR_LANES;
-constexpr int DR_TILE = 16;                  // tokens staged at once
+constexpr int DR_COLS = 8;                   // columns of the state per block: one warp each
+constexpr int DR_THREADS = DR_COLS * 32;
+constexpr int DR_TILE = 16;                  // tokens solved at once
 constexpr int DR_MAX_DIM = 256;
-
-__device__ __forceinline__ float group_sum(float v) {
-  v += __shfl_xor_sync(0xffffffffu, v, 1);
-  v += __shfl_xor_sync(0xffffffffu, v, 2);
-  v += __shfl_xor_sync(0xffffffffu, v, 4);
-  return v;
-}
 
 __device__ __forceinline__ float softplus_f32(float z) { return z > 20.f ? z : log1pf(expf(z)); }
 
@@ -113,19 +105,56 @@ struct DeltaArgs {
   int b_off, a_off;                // columns of head 0's write strength and decay inputs
   int heads, qk_heads, dim, vdim;
   int write_state;
+  int vec;                         // rows of q and k can be fetched in 16-byte pieces
 };
 
-// R: state entries per lane (dim <= DR_LANES * R)
+// A tile's queries and keys on their way from global memory to shared memory: fetched into registers one tile ahead, so
+// that the loads are in flight while the tile before is being solved.
+template <typename T, int R>
+struct TileFetch {
+  static constexpr int VEC = 16 / sizeof(T);
+  static constexpr int ROW = 32 * R / VEC;                                   // pieces per row of q (or k)
+  static constexpr int QK = 2 * DR_TILE * ROW;
+  static constexpr int PER = (QK + DR_THREADS - 1) / DR_THREADS;
+  uint4 qk[PER];
+};
+template <typename T> __device__ __forceinline__ void unpack16(const uint4& raw, float* dst);
+template <> __device__ __forceinline__ void unpack16<float>(const uint4& raw, float* dst) {
+  dst[0] = __uint_as_float(raw.x); dst[1] = __uint_as_float(raw.y); dst[2] = __uint_as_float(raw.z); dst[3] = __uint_as_float(raw.w);
+}
+template <> __device__ __forceinline__ void unpack16<__nv_bfloat16>(const uint4& raw, float* dst) {
+  const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    dst[2 * i] = __uint_as_float(w[i] << 16);
+    dst[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+  }
+}
+
+// R: state entries per lane (dim <= 32 * R).
+//
+// A tile of up to DR_TILE tokens is solved at once.  With L_t the sum of log g over the tile's tokens up to t and S_0
+// the state in front of the tile,
+//     u_t = beta_t (v_t - e^{L_t} S_0^T k_t) - sum_{j<t} A[t][j] u_j,      A[t][j] = beta_t e^{L_t - L_j} (k_j . k_t)
+//     o_t = e^{L_t} S_0^T q_t + sum_{j<=t} B[t][j] u_j,                    B[t][j] = e^{L_t - L_j} (k_j . q_t)
+//     S   = e^{L_last} S_0 + sum_j e^{L_last - L_j} k_j u_j^T
+// which is the recurrence written out.  A and B are the same for every column and are computed once per block.  A warp
+// owns one column: its lanes share the column's entries, the 32 products S_0^T k_t and S_0^T q_t are reduced across
+// the lanes so that lane t ends with the first of token t and lane 16 + t with the second, and one loop over j then
+// broadcasts u_j from lane j, lets the lanes below 16 finish their u_t, those above their o_t, and all of them add
+// k_j u_j to their entries of S.
 template <typename T, int R>
 __global__ void __launch_bounds__(DR_THREADS)
 delta_rule_kernel(const T* __restrict__ qkv, const T* __restrict__ ba, const float* __restrict__ a_log,
                   const float* __restrict__ dt_bias, float* __restrict__ state, const int* __restrict__ cu_tokens,
                   const int* __restrict__ slots, float* __restrict__ out, DeltaArgs p) {
-  constexpr int DP = DR_LANES * R;           // padded key size
+  constexpr int DP = 32 * R + 1;             // padded key size; odd, so that rows of a tile start in different banks
   extern __shared__ float smem[];
   float* q_s = smem;                         // [DR_TILE][DP]
   float* k_s = q_s + DR_TILE * DP;           // [DR_TILE][DP]
-  __shared__ float v_s[DR_TILE][DR_COLS], o_s[DR_TILE][DR_COLS], beta_s[DR_TILE], g_s[DR_TILE];
+  __shared__ float v_s[DR_TILE][DR_COLS], o_s[DR_TILE][DR_COLS], beta_s[DR_TILE], raw_s[DR_TILE], lg_s[DR_TILE], el_s[DR_TILE],
+      er_s[DR_TILE];
+  __shared__ float C_s[2 * DR_TILE][DR_TILE + 1];      // rows t: -A[t][.]; rows 16 + t: B[t][.]
   const int req = blockIdx.z, h = blockIdx.y, col0 = blockIdx.x * DR_COLS;
   const int begin = cu_tokens[req], count = cu_tokens[req + 1] - begin;
   const int slot = slots[req];
@@ -133,79 +162,206 @@ delta_rule_kernel(const T* __restrict__ qkv, const T* __restrict__ ba, const flo
   pdl_launch_dependents();
   if (count <= 0) return;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int grp = tid / DR_LANES, lg = tid % DR_LANES;
-  const int col = col0 + grp;
+  const int col = col0 + warp;
   const int kh = h / (p.heads / p.qk_heads);
   const int dim = p.dim, vdim = p.vdim;
   float* sp = state + (((long long)slot * p.heads + h) * dim) * vdim + col;
   float S[R];
 #pragma unroll
   for (int r = 0; r < R; ++r) {
-    const int i = lg + DR_LANES * r;
+    const int i = lane + 32 * r;
     S[r] = (i < dim && col < vdim) ? sp[(long long)i * vdim] : 0.f;
   }
   const float rate = expf(a_log[h]), bias = dt_bias[h];
   const float q_scale = 1.0f / sqrtf((float)dim);
+  if (count == 1) {
+    // a decoded token: the recurrence itself, every warp on its own (no tables, no barriers)
+    const T* row = qkv + (long long)begin * p.ld_qkv + (long long)kh * dim;
+    float kk[R], qq[R];
+    float sk = 0.f, sq = 0.f;
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      const int i = lane + 32 * r;
+      kk[r] = i < dim ? to_f32<T>(row[p.k_off + i]) : 0.f;
+      qq[r] = i < dim ? to_f32<T>(row[p.q_off + i]) : 0.f;
+      sk = fmaf(kk[r], kk[r], sk);
+      sq = fmaf(qq[r], qq[r], sq);
+    }
+    const float k_scale = 1.0f / sqrtf(warp_sum(sk) + 1e-6f), qn_scale = q_scale / sqrtf(warp_sum(sq) + 1e-6f);
+    float pk = 0.f, pq = 0.f, kq = 0.f;
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      kk[r] *= k_scale;
+      qq[r] *= qn_scale;
+      pk = fmaf(S[r], kk[r], pk);
+      pq = fmaf(S[r], qq[r], pq);
+      kq = fmaf(kk[r], qq[r], kq);
+    }
+    pk = warp_sum(pk); pq = warp_sum(pq); kq = warp_sum(kq);
+    const T* gates = ba + (long long)begin * p.ld_ba;
+    const float beta = 1.f / (1.f + expf(-to_f32<T>(gates[p.b_off + h])));
+    const float g = expf(-rate * softplus_f32(to_f32<T>(gates[p.a_off + h]) + bias));
+    const float v = col < vdim ? to_f32<T>(qkv[(long long)begin * p.ld_qkv + p.v_off + (long long)h * vdim + col]) : 0.f;
+    const float u = beta * (v - g * pk);
+    if (lane == 0 && col < vdim) out[(long long)begin * p.ld_out + (long long)h * vdim + col] = fmaf(kq, u, g * pq);
+    if (p.write_state) {
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+        const int i = lane + 32 * r;
+        if (i < dim && col < vdim) sp[(long long)i * vdim] = fmaf(kk[r], u, g * S[r]);
+      }
+    }
+    return;
+  }
+  using F = TileFetch<T, R>;
+  F pf;
+  auto fetch = [&](int first) {
+    const int rows = min(DR_TILE, count - first);
+    const long long at = begin + first;
+#pragma unroll
+    for (int i = 0; i < F::PER; ++i) {
+      const int pi = tid + i * DR_THREADS;
+      const int which = pi / (DR_TILE * F::ROW), rem = pi - which * (DR_TILE * F::ROW);
+      const int t = rem / F::ROW, c = (rem - t * F::ROW) * F::VEC;
+      pf.qk[i] = make_uint4(0u, 0u, 0u, 0u);
+      if (pi < F::QK && t < rows && c < dim)
+        pf.qk[i] = *reinterpret_cast<const uint4*>(qkv + (at + t) * p.ld_qkv + (which ? p.k_off : p.q_off) + (long long)kh * dim + c);
+    }
+  };
+  if (p.vec) fetch(0);
 
   for (int tile0 = 0; tile0 < count; tile0 += DR_TILE) {
     const int tt = min(DR_TILE, count - tile0);
     const long long tok0 = begin + tile0;
-    for (int e = tid; e < tt * DP; e += DR_THREADS) {
-      const int t = e / DP, d = e - t * DP;
-      const T* row = qkv + (tok0 + t) * p.ld_qkv + (long long)kh * dim + d;
-      q_s[e] = d < dim ? to_f32<T>(row[p.q_off]) : 0.f;
-      k_s[e] = d < dim ? to_f32<T>(row[p.k_off]) : 0.f;
+    if (p.vec) {
+      // this tile's queries and keys are in registers already; the next tile's are requested before this one is used
+#pragma unroll
+      for (int i = 0; i < F::PER; ++i) {
+        const int pi = tid + i * DR_THREADS;
+        if (pi < F::QK) {
+          const int which = pi / (DR_TILE * F::ROW), rem = pi - which * (DR_TILE * F::ROW);
+          const int t = rem / F::ROW, c = (rem - t * F::ROW) * F::VEC;
+          float vals[F::VEC];
+          unpack16<T>(pf.qk[i], vals);
+          float* dst = (which ? k_s : q_s) + t * DP + c;
+#pragma unroll
+          for (int e = 0; e < F::VEC; ++e) dst[e] = vals[e];
+        }
+      }
+      if (tile0 + DR_TILE < count) fetch(tile0 + DR_TILE);
+    } else {
+      for (int e = tid; e < DR_TILE * DP; e += DR_THREADS) {
+        const int t = e / DP, d = e - t * DP;
+        const bool in = t < tt && d < dim;
+        const T* row = qkv + (tok0 + (in ? t : 0)) * p.ld_qkv + (long long)kh * dim + (in ? d : 0);
+        q_s[e] = in ? to_f32<T>(row[p.q_off]) : 0.f;
+        k_s[e] = in ? to_f32<T>(row[p.k_off]) : 0.f;
+      }
     }
-    for (int e = tid; e < tt * DR_COLS; e += DR_THREADS) {
-      const int t = e / DR_COLS, c = e - t * DR_COLS;
-      v_s[t][c] = col0 + c < vdim ? to_f32<T>(qkv[(tok0 + t) * p.ld_qkv + p.v_off + (long long)h * vdim + col0 + c]) : 0.f;
-    }
-    if (tid < tt) {
-      const T* row = ba + (tok0 + tid) * p.ld_ba;
-      beta_s[tid] = 1.f / (1.f + expf(-to_f32<T>(row[p.b_off + h])));
-      g_s[tid] = expf(-rate * softplus_f32(to_f32<T>(row[p.a_off + h]) + bias));
+    if (tid < DR_TILE * DR_COLS) {
+      const int t = tid / DR_COLS, c = tid - t * DR_COLS;
+      v_s[t][c] = (t < tt && col0 + c < vdim) ? to_f32<T>(qkv[(tok0 + t) * p.ld_qkv + p.v_off + (long long)h * vdim + col0 + c]) : 0.f;
+    } else if (tid < DR_TILE * DR_COLS + tt) {
+      const int t = tid - DR_TILE * DR_COLS;
+      const T* row = ba + (tok0 + t) * p.ld_ba;
+      beta_s[t] = 1.f / (1.f + expf(-to_f32<T>(row[p.b_off + h])));
+      raw_s[t] = -rate * softplus_f32(to_f32<T>(row[p.a_off + h]) + bias);          // log g
     }
     __syncthreads();
-    for (int vid = warp; vid < 2 * tt; vid += DR_THREADS / 32) {
+    for (int vid = warp; vid < 2 * tt; vid += DR_COLS) {
       float* vec = vid < tt ? q_s + vid * DP : k_s + (vid - tt) * DP;
       float ss = 0.f;
       for (int d = lane; d < dim; d += 32) ss = fmaf(vec[d], vec[d], ss);
       const float scale = (vid < tt ? q_scale : 1.f) / sqrtf(warp_sum(ss) + 1e-6f);
       for (int d = lane; d < dim; d += 32) vec[d] *= scale;
     }
-    __syncthreads();
-    for (int t = 0; t < tt; ++t) {
-      const float* kt = k_s + t * DP + lg;
-      const float* qt = q_s + t * DP + lg;
-      float kk[R];
-      float s = 0.f;
-#pragma unroll
-      for (int r = 0; r < R; ++r) {
-        kk[r] = kt[DR_LANES * r];
-        s = fmaf(S[r], kk[r], s);
+    if (tid < tt) {                           // L_t, e^{L_t} and e^{L_last - L_t}
+      float mine = 0.f, all = 0.f;
+      for (int t = 0; t < tt; ++t) {
+        all += raw_s[t];
+        if (t == tid) mine = all;
       }
-      s = group_sum(s);
-      const float g = g_s[t];
-      const float u = beta_s[t] * (v_s[t][grp] - g * s);
-      float o = 0.f;
-#pragma unroll
-      for (int r = 0; r < R; ++r) {
-        S[r] = fmaf(kk[r], u, g * S[r]);
-        o = fmaf(S[r], qt[DR_LANES * r], o);
-      }
-      o = group_sum(o);
-      if (lg == 0) o_s[t][grp] = o;
+      lg_s[tid] = mine;
+      el_s[tid] = expf(mine);
+      er_s[tid] = expf(all - mine);
     }
     __syncthreads();
-    for (int e = tid; e < tt * DR_COLS; e += DR_THREADS) {
-      const int t = e / DR_COLS, c = e - t * DR_COLS;
+    // the tables: thread e takes the pair (t, j) = (e / 16, e % 16) of A, thread 256 + e that of B
+    for (int e = tid; e < 2 * DR_TILE * DR_TILE; e += DR_THREADS) {
+      const int row = e / DR_TILE, j = e - row * DR_TILE;
+      const int t = row & (DR_TILE - 1);
+      const bool second = row >= DR_TILE;
+      float c = 0.f;
+      if (t < tt && (second ? j <= t : j < t)) {
+        const float* kj = k_s + j * DP;
+        const float* xt = (second ? q_s : k_s) + t * DP;
+        float d0 = 0.f, d1 = 0.f;
+        int d = 0;
+        for (; d + 1 < dim; d += 2) {
+          d0 = fmaf(kj[d], xt[d], d0);
+          d1 = fmaf(kj[d + 1], xt[d + 1], d1);
+        }
+        if (d < dim) d0 = fmaf(kj[d], xt[d], d0);
+        const float dec = expf(lg_s[t] - lg_s[j]);
+        c = second ? dec * (d0 + d1) : -beta_s[t] * dec * (d0 + d1);
+      }
+      C_s[row][j] = c;
+    }
+    // S_0^T k_t (values 0..15) and S_0^T q_t (values 16..31) for this column: partial sums per lane, then a
+    // reduction across the lanes that leaves value l complete in lane l
+    float val[2 * DR_TILE];
+#pragma unroll
+    for (int t = 0; t < DR_TILE; ++t) {
+      float sk = 0.f, sq = 0.f;
+      const float* kt = k_s + t * DP + lane;
+      const float* qt = q_s + t * DP + lane;
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+        sk = fmaf(S[r], kt[32 * r], sk);
+        sq = fmaf(S[r], qt[32 * r], sq);
+      }
+      val[t] = sk;
+      val[DR_TILE + t] = sq;
+    }
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) {
+      const bool upper = (lane & off) != 0;
+#pragma unroll
+      for (int i = 0; i < off; ++i) {
+        const float send = upper ? val[i] : val[i + off];
+        const float keep = upper ? val[i + off] : val[i];
+        val[i] = keep + __shfl_xor_sync(0xffffffffu, send, off);
+      }
+    }
+    __syncthreads();
+    const int t_mine = lane & (DR_TILE - 1);
+    float x = 0.f;
+    if (t_mine < tt) x = lane < DR_TILE ? beta_s[t_mine] * (v_s[t_mine][warp] - el_s[t_mine] * val[0]) : el_s[t_mine] * val[0];
+    const float carry = el_s[tt - 1];
+#pragma unroll
+    for (int r = 0; r < R; ++r) S[r] *= carry;
+#pragma unroll
+    for (int j = 0; j < DR_TILE; ++j) {
+      if (j < tt) {
+        const float uj = __shfl_sync(0xffffffffu, x, j);
+        x = fmaf(C_s[lane][j], uj, x);
+        const float w = uj * er_s[j];
+        const float* kj = k_s + j * DP + lane;
+#pragma unroll
+        for (int r = 0; r < R; ++r) S[r] = fmaf(kj[32 * r], w, S[r]);
+      }
+    }
+    if (lane >= DR_TILE && t_mine < tt) o_s[t_mine][warp] = x;
+    __syncthreads();
+    if (tid < tt * DR_COLS) {
+      const int t = tid / DR_COLS, c = tid - t * DR_COLS;
       if (col0 + c < vdim) out[(tok0 + t) * p.ld_out + (long long)h * vdim + col0 + c] = o_s[t][c];
     }
   }
   if (p.write_state) {
 #pragma unroll
     for (int r = 0; r < R; ++r) {
-      const int i = lg + DR_LANES * r;
+      const int i = lane + 32 * r;
       if (i < dim && col < vdim) sp[(long long)i * vdim] = S[r];
     }
   }
@@ -214,7 +370,7 @@ delta_rule_kernel(const T* __restrict__ qkv, const T* __restrict__ ba, const flo
 template <typename T, int R>
 int launch_delta_r(const void* qkv, const void* ba, const float* a_log, const float* dt_bias, float* state,
                    const int* cu_tokens, const int* slots, float* out, const DeltaArgs& p, int requests, cudaStream_t stream) {
-  const size_t smem = (size_t)2 * DR_TILE * DR_LANES * R * sizeof(float);
+  const size_t smem = (size_t)2 * DR_TILE * (32 * R + 1) * sizeof(float);
   hfee_launch(delta_rule_kernel<T, R>, dim3((unsigned)((p.vdim + DR_COLS - 1) / DR_COLS), (unsigned)p.heads, (unsigned)requests),
               dim3(DR_THREADS), smem, stream, (const T*)qkv, (const T*)ba, a_log, dt_bias, state, cu_tokens, slots, out, p);
   return hfee_check_launch("delta_rule");
@@ -223,13 +379,11 @@ int launch_delta_r(const void* qkv, const void* ba, const float* a_log, const fl
 template <typename T>
 int launch_delta(const void* qkv, const void* ba, const float* a_log, const float* dt_bias, float* state,
                  const int* cu_tokens, const int* slots, float* out, const DeltaArgs& p, int requests, cudaStream_t stream) {
-  const int r = (p.dim + DR_LANES - 1) / DR_LANES;
+  const int r = (p.dim + 31) / 32;
   if (r <= 1) return launch_delta_r<T, 1>(qkv, ba, a_log, dt_bias, state, cu_tokens, slots, out, p, requests, stream);
   if (r <= 2) return launch_delta_r<T, 2>(qkv, ba, a_log, dt_bias, state, cu_tokens, slots, out, p, requests, stream);
   if (r <= 4) return launch_delta_r<T, 4>(qkv, ba, a_log, dt_bias, state, cu_tokens, slots, out, p, requests, stream);
-  if (r <= 8) return launch_delta_r<T, 8>(qkv, ba, a_log, dt_bias, state, cu_tokens, slots, out, p, requests, stream);
-  if (r <= 16) return launch_delta_r<T, 16>(qkv, ba, a_log, dt_bias, state, cu_tokens, slots, out, p, requests, stream);
-  return launch_delta_r<T, 32>(qkv, ba, a_log, dt_bias, state, cu_tokens, slots, out, p, requests, stream);
+  return launch_delta_r<T, 8>(qkv, ba, a_log, dt_bias, state, cu_tokens, slots, out, p, requests, stream);
 }
 
 }  // namespace
@@ -266,7 +420,10 @@ HFEE_API int hfee_delta_rule(const void* qkv, long long ld_qkv, int q_off, int k
   if (requests == 0) return HFEE_OK;
   HFEE_REQUIRE(heads > 0 && qk_heads > 0 && heads % qk_heads == 0, "delta_rule: heads %d must be a multiple of %d", heads, qk_heads);
   HFEE_REQUIRE(dim > 0 && dim <= DR_MAX_DIM && vdim > 0, "delta_rule: key size %d is outside 1..%d", dim, DR_MAX_DIM);
-  DeltaArgs p{ld_qkv, ld_ba, ld_out, q_off, k_off, v_off, b_off, a_off, heads, qk_heads, dim, vdim, write_state};
+  const int vec_elems = dtype == HFEE_F32 ? 4 : 8;
+  const int vec = dim % vec_elems == 0 && ld_qkv % vec_elems == 0 && q_off % vec_elems == 0 && k_off % vec_elems == 0 &&
+                  (uintptr_t)qkv % 16 == 0;
+  DeltaArgs p{ld_qkv, ld_ba, ld_out, q_off, k_off, v_off, b_off, a_off, heads, qk_heads, dim, vdim, write_state, vec};
   if (dtype == HFEE_F32)
     return launch_delta<float>(qkv, ba, a_log, dt_bias, state, cu_tokens, slots, out, p, requests, stream);
   if (dtype == HFEE_BF16)

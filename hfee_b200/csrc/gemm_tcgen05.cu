@@ -41,7 +41,7 @@ constexpr int EPI_WARPS = 8;
 constexpr int ACC_STAGES = 2;
 constexpr int SK_MAX_PIECES = 4;      // a tile is cut into at most this many ranges of K blocks
 
-enum Epilogue { EPI_STORE = 0, EPI_ACCUM = 1, EPI_SWIGLU = 2, EPI_ROPE = 3, EPI_GEGLU = 4 };
+enum Epilogue { EPI_STORE = 0, EPI_ACCUM = 1, EPI_SWIGLU = 2, EPI_ROPE = 3, EPI_GEGLU = 4, EPI_RELU2 = 5 };   // 5: store relu(x)^2
 
 template <int BN> struct TileCfg {
   static constexpr int STAGES = BN == 128 ? 6 : 4;
@@ -305,6 +305,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           }
         } else {
           TOut* dst = C + (long long)row * ldc + col0;
+          if constexpr (EPI == EPI_RELU2) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const float t = fmaxf(__uint_as_float(v[j]), 0.f);
+              v[j] = __float_as_uint(t * t);
+            }
+          }
           const bool full = col0 + 32 <= N && (((uintptr_t)dst) & 15) == 0;
           if (full) {
             if constexpr (sizeof(TOut) == 4) {
@@ -454,6 +461,10 @@ int dispatch(const CUtensorMap& ma, const CUtensorMap& mw, void* C, long long ld
     if (epilogue == EPI_GEGLU) return launch<BN, EPI_GEGLU, __nv_bfloat16>(ma, mw, C, ldc, M, N, K, status, ws, ws_floats, flags, stream);
     return launch<BN, EPI_SWIGLU, __nv_bfloat16>(ma, mw, C, ldc, M, N, K, status, ws, ws_floats, flags, stream);
   }
+  if (epilogue == EPI_RELU2) {
+    if (out_dtype != HFEE_BF16) return hfee_fail(HFEE_ERR_ARG, "gemm_tcgen05: the relu^2 epilogue writes bfloat16");
+    return launch<BN, EPI_RELU2, __nv_bfloat16>(ma, mw, C, ldc, M, N, K, status, ws, ws_floats, flags, stream);
+  }
   if (out_dtype == HFEE_BF16) return launch<BN, EPI_STORE, __nv_bfloat16>(ma, mw, C, ldc, M, N, K, status, ws, ws_floats, flags, stream);
   return launch<BN, EPI_STORE, float>(ma, mw, C, ldc, M, N, K, status, ws, ws_floats, flags, stream);
 }
@@ -474,7 +485,7 @@ HFEE_API int hfee_gemm_tcgen05(const void* A, long long lda, const void* W, long
   HFEE_REQUIRE(lda % 8 == 0 && ldw % 8 == 0 && lda >= K && ldw >= K,
                "gemm_tcgen05: leading dimensions (%lld, %lld) must be multiples of 8 and at least K", lda, ldw);
   HFEE_REQUIRE(((uintptr_t)A % 16 == 0) && ((uintptr_t)W % 16 == 0), "gemm_tcgen05: operands must be 16-byte aligned");
-  HFEE_REQUIRE((epilogue >= 0 && epilogue <= 2) || epilogue == EPI_GEGLU, "gemm_tcgen05: unknown epilogue %d", epilogue);
+  HFEE_REQUIRE((epilogue >= 0 && epilogue <= 2) || epilogue == EPI_GEGLU || epilogue == EPI_RELU2, "gemm_tcgen05: unknown epilogue %d", epilogue);
   HFEE_REQUIRE((epilogue != EPI_SWIGLU && epilogue != EPI_GEGLU) || N % 8 == 0, "gemm_tcgen05: SwiGLU needs N %% 8 == 0, got %d", N);
   HFEE_REQUIRE(ldc >= ((epilogue == EPI_SWIGLU || epilogue == EPI_GEGLU) ? N / 2 : N), "gemm_tcgen05: ldc=%lld is too small", ldc);
   HFEE_REQUIRE(block_n == 128 || block_n == 192 || block_n == 256, "gemm_tcgen05: block_n must be 128, 192 or 256");

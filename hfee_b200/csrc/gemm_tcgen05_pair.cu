@@ -40,7 +40,7 @@ template <int BN> struct PairCfg {
   static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 + EPI_BYTES;
 };
 
-enum Epilogue { EPI_STORE = 0, EPI_ACCUM = 1, EPI_SWIGLU = 2, EPI_ROPE = 3, EPI_GEGLU = 4 };
+enum Epilogue { EPI_STORE = 0, EPI_ACCUM = 1, EPI_SWIGLU = 2, EPI_ROPE = 3, EPI_GEGLU = 4, EPI_RELU2 = 5 };   // 5: store relu(x)^2
 
 __device__ __forceinline__ uint32_t cluster_rank() {
   uint32_t r;
@@ -252,6 +252,13 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           }
         } else {
           TOut* dst = C + (long long)row * ldc + col0;
+          if constexpr (EPI == EPI_RELU2) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const float t = fmaxf(__uint_as_float(v[j]), 0.f);
+              v[j] = __float_as_uint(t * t);
+            }
+          }
           const bool full = col0 + 32 <= N && (((uintptr_t)dst) & 15) == 0;
           if (full && sizeof(TOut) == 4) {
 #pragma unroll
@@ -382,7 +389,7 @@ HFEE_API int hfee_gemm_tcgen05_pair(const void* A, long long lda, const void* W,
   HFEE_REQUIRE(lda % 8 == 0 && ldw % 8 == 0 && lda >= K && ldw >= K,
                "gemm_tcgen05_pair: leading dimensions (%lld, %lld) must be multiples of 8 and at least K", lda, ldw);
   HFEE_REQUIRE(((uintptr_t)A % 16 == 0) && ((uintptr_t)W % 16 == 0), "gemm_tcgen05_pair: operands must be 16-byte aligned");
-  HFEE_REQUIRE((epilogue >= 0 && epilogue <= 2) || epilogue == EPI_GEGLU, "gemm_tcgen05_pair: unknown epilogue %d", epilogue);
+  HFEE_REQUIRE((epilogue >= 0 && epilogue <= 2) || epilogue == EPI_GEGLU || epilogue == EPI_RELU2, "gemm_tcgen05_pair: unknown epilogue %d", epilogue);
   HFEE_REQUIRE((epilogue != EPI_SWIGLU && epilogue != EPI_GEGLU) || N % 8 == 0, "gemm_tcgen05_pair: SwiGLU needs N %% 8 == 0, got %d", N);
   HFEE_REQUIRE(ldc >= ((epilogue == EPI_SWIGLU || epilogue == EPI_GEGLU) ? N / 2 : N), "gemm_tcgen05_pair: ldc=%lld is too small", ldc);
   CUtensorMap ma, mw;
@@ -398,6 +405,10 @@ HFEE_API int hfee_gemm_tcgen05_pair(const void* A, long long lda, const void* W,
     if (out_dtype != HFEE_BF16) return hfee_fail(HFEE_ERR_ARG, "gemm_tcgen05_pair: the gated epilogues write bfloat16");
     if (epilogue == EPI_GEGLU) return launch_pair<256, EPI_GEGLU, __nv_bfloat16>(ma, mw, C, ldc, M, N, K, status, stream);
     return launch_pair<256, EPI_SWIGLU, __nv_bfloat16>(ma, mw, C, ldc, M, N, K, status, stream);
+  }
+  if (epilogue == EPI_RELU2) {
+    HFEE_REQUIRE(out_dtype == HFEE_BF16, "gemm_tcgen05_pair: the relu^2 epilogue writes bfloat16");
+    return launch_pair<256, EPI_RELU2, __nv_bfloat16>(ma, mw, C, ldc, M, N, K, status, stream);
   }
   if (out_dtype == HFEE_BF16) return launch_pair<256, EPI_STORE, __nv_bfloat16>(ma, mw, C, ldc, M, N, K, status, stream);
   return launch_pair<256, EPI_STORE, float>(ma, mw, C, ldc, M, N, K, status, stream);

@@ -53,20 +53,23 @@ __device__ __forceinline__ float la_exp2(float x) {
   return y;
 }
 
-// NG: groups of 16 value columns per warp (dv <= 64 * NG)
-template <int NG>
-__global__ void __launch_bounds__(LA_THREADS)
+// NG: groups of 16 value columns per warp (dv <= 64 * NG).  WG: sets of four warps; each set owns LA_ROWS rows of the
+// tile and works as described above, and all sets share the key blocks in shared memory (half the cache traffic per row
+// and twice the warps per block with two sets).
+template <int NG, int WG>
+__global__ void __launch_bounds__(LA_THREADS * WG)
 latent_attention_kernel(LatentParams p) {
+  constexpr int ROWS = LA_ROWS * WG, THREADS = LA_THREADS * WG;
   extern __shared__ __align__(16) unsigned char la_smem[];
   const int dk = p.dk, dv = p.dv, ldk = dk + LA_PAD;
   bf16* Qs = reinterpret_cast<bf16*>(la_smem);                // [LA_ROWS][ldk]
-  bf16* Ks = Qs + LA_ROWS * ldk;                              // [2][LA_BN][ldk]
-  bf16* Ps = Ks + 2 * LA_BN * ldk;                            // [LA_ROWS][LA_PS_LD]
-  float* m_s = reinterpret_cast<float*>(Ps + LA_ROWS * LA_PS_LD);
-  float* l_s = m_s + LA_ROWS;
-  float* wmax = l_s + LA_ROWS;                                // [LA_WARPS][LA_ROWS]
-  float* wsum = wmax + LA_WARPS * LA_ROWS;                    // [LA_WARPS][LA_ROWS]
-  int* rowpos = reinterpret_cast<int*>(wsum + LA_WARPS * LA_ROWS);   // position of the row's token, -1: no row
+  bf16* Ks = Qs + ROWS * ldk;                                 // [2][LA_BN][ldk]
+  bf16* Ps = Ks + 2 * LA_BN * ldk;                            // [ROWS][LA_PS_LD]
+  float* m_s = reinterpret_cast<float*>(Ps + ROWS * LA_PS_LD);
+  float* l_s = m_s + ROWS;
+  float* wmax = l_s + ROWS;                                   // [LA_WARPS][ROWS]
+  float* wsum = wmax + LA_WARPS * ROWS;                       // [LA_WARPS][ROWS]
+  int* rowpos = reinterpret_cast<int*>(wsum + LA_WARPS * ROWS);      // position of the row's token, -1: no row
 
   const int req = blockIdx.z, head0 = blockIdx.y * p.rows_per_token;
   const int begin = p.cu_tokens[req], count = p.cu_tokens[req + 1] - begin;     // host-written batch layout
@@ -76,13 +79,14 @@ latent_attention_kernel(LatentParams p) {
   if (t0 >= count) return;
   const int tokens = min(p.tokens_per_tile, count - t0);
   const int slot = p.slots[req], before = p.context_before[req];
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int tid = threadIdx.x, warp = (tid >> 5) % LA_WARPS, lane = tid & 31;
+  const int rb = (tid >> 5) / LA_WARPS * LA_ROWS;              // first row of this set of warps
   const int p_first = before + t0, p_last = before + t0 + tokens - 1;
   const int lo = p.window > 0 ? max(0, p_first - p.window + 1) : 0;
   const int* table = p.block_table + (long long)slot * p.max_pages;
   const long long page_stride = (long long)(p.page_mask + 1) * dk;
 
-  if (tid < LA_ROWS) {
+  if (tid < ROWS) {
     const int t = tid / p.rows_per_token, h = head0 + tid % p.rows_per_token;
     rowpos[tid] = (t < tokens && h < p.heads) ? before + t0 + t : -1;
     m_s[tid] = -INFINITY;
@@ -90,7 +94,7 @@ latent_attention_kernel(LatentParams p) {
   }
   // queries of the tile
   const int pieces = dk >> 3;
-  for (int e = tid; e < LA_ROWS * pieces; e += LA_THREADS) {
+  for (int e = tid; e < ROWS * pieces; e += THREADS) {
     const int r = e / pieces, c = (e - r * pieces) * 8;
     const int t = r / p.rows_per_token, h = head0 + r % p.rows_per_token;
     const bool valid = t < tokens && h < p.heads;
@@ -99,7 +103,7 @@ latent_attention_kernel(LatentParams p) {
   }
   auto load_block = [&](int block_start, int buf) {
     bf16* dst = Ks + (long long)buf * LA_BN * ldk;
-    for (int e = tid; e < LA_BN * pieces; e += LA_THREADS) {
+    for (int e = tid; e < LA_BN * pieces; e += THREADS) {
       const int r = e / pieces, c = (e - r * pieces) * 8;
       const int kp = block_start + r;
       const bool valid = kp >= lo && kp <= p_last;
@@ -142,8 +146,8 @@ latent_attention_kernel(LatentParams p) {
         for (int c = 0; c < 4; ++c) s[a][b][c] = 0.f;
     for (int k0 = 0; k0 < dk; k0 += 16) {
       uint32_t a0[4], a1[4], b[4];
-      load_a(a0, Qs, ldk, 0, k0, lane);
-      load_a(a1, Qs, ldk, 16, k0, lane);
+      load_a(a0, Qs, ldk, rb, k0, lane);
+      load_a(a1, Qs, ldk, rb + 16, k0, lane);
       load_b_pair(b, Kb, ldk, 16 * warp, k0, lane);
       mma_bf16(s[0][0], a0, b[0], b[1]);
       mma_bf16(s[0][1], a0, b[2], b[3]);
@@ -156,7 +160,7 @@ latent_attention_kernel(LatentParams p) {
     for (int mt = 0; mt < 2; ++mt)
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
-        const int pos = rowpos[mt * 16 + quad_row + 8 * half];
+        const int pos = rowpos[rb + mt * 16 + quad_row + 8 * half];
         const int low = p.window > 0 ? pos - p.window + 1 : 0;
         float mx = -INFINITY;
 #pragma unroll
@@ -172,7 +176,7 @@ latent_attention_kernel(LatentParams p) {
         mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
         mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
         rmax[mt][half] = mx;
-        if ((lane & 3) == 0) wmax[warp * LA_ROWS + mt * 16 + quad_row + 8 * half] = mx;
+        if ((lane & 3) == 0) wmax[warp * ROWS + rb + mt * 16 + quad_row + 8 * half] = mx;
       }
     __syncthreads();
     // weights against the new row maximum; the factor the old sums and outputs shrink by
@@ -181,11 +185,11 @@ latent_attention_kernel(LatentParams p) {
     for (int mt = 0; mt < 2; ++mt)
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
-        const int row = mt * 16 + quad_row + 8 * half;
+        const int row = rb + mt * 16 + quad_row + 8 * half;
         const float m_old = m_s[row];
         float m_new = m_old;
 #pragma unroll
-        for (int w = 0; w < LA_WARPS; ++w) m_new = fmaxf(m_new, wmax[w * LA_ROWS + row]);
+        for (int w = 0; w < LA_WARPS; ++w) m_new = fmaxf(m_new, wmax[w * ROWS + row]);
         const float m_use = m_new == -INFINITY ? 0.f : m_new;
         alpha[mt][half] = la_exp2(m_old - m_use);           // 2^-inf = 0 while the row has seen no key
         float sum = 0.f;
@@ -199,16 +203,16 @@ latent_attention_kernel(LatentParams p) {
         }
         sum += __shfl_xor_sync(0xffffffffu, sum, 1);
         sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-        if ((lane & 3) == 0) wsum[warp * LA_ROWS + row] = sum;
+        if ((lane & 3) == 0) wsum[warp * ROWS + row] = sum;
       }
     __syncthreads();
-    if (tid < LA_ROWS) {
+    if (tid < ROWS) {
       const float m_old = m_s[tid];
       float m_new = m_old, sum = 0.f;
 #pragma unroll
       for (int w = 0; w < LA_WARPS; ++w) {
-        m_new = fmaxf(m_new, wmax[w * LA_ROWS + tid]);
-        sum += wsum[w * LA_ROWS + tid];
+        m_new = fmaxf(m_new, wmax[w * ROWS + tid]);
+        sum += wsum[w * ROWS + tid];
       }
       const float m_use = m_new == -INFINITY ? 0.f : m_new;
       l_s[tid] = l_s[tid] * la_exp2(m_old - m_use) + sum;
@@ -231,8 +235,8 @@ latent_attention_kernel(LatentParams p) {
 #pragma unroll
       for (int k0 = 0; k0 < LA_BN; k0 += 16) {
         uint32_t a0[4], a1[4], b[4];
-        load_a(a0, Ps, LA_PS_LD, 0, k0, lane);
-        load_a(a1, Ps, LA_PS_LD, 16, k0, lane);
+        load_a(a0, Ps, LA_PS_LD, rb, k0, lane);
+        load_a(a1, Ps, LA_PS_LD, rb + 16, k0, lane);
         la_ldmatrix_x4_trans(b, Kb + (k0 + (lane & 7) + ((lane >> 3) & 1) * 8) * ldk + 16 * grp + (lane >> 4) * 8);
         mma_bf16(o[g][0][0], a0, b[0], b[1]);
         mma_bf16(o[g][1][0], a0, b[2], b[3]);
@@ -246,7 +250,7 @@ latent_attention_kernel(LatentParams p) {
   for (int mt = 0; mt < 2; ++mt)
 #pragma unroll
     for (int half = 0; half < 2; ++half) {
-      const int row = mt * 16 + quad_row + 8 * half;
+      const int row = rb + mt * 16 + quad_row + 8 * half;
       if (rowpos[row] < 0) continue;
       const int t = row / p.rows_per_token, h = head0 + row % p.rows_per_token;
       const float l = l_s[row];
@@ -264,19 +268,19 @@ latent_attention_kernel(LatentParams p) {
     }
 }
 
-size_t latent_smem(int dk) {
-  return (size_t)(LA_ROWS + 2 * LA_BN) * (dk + LA_PAD) * sizeof(bf16) + (size_t)LA_ROWS * LA_PS_LD * sizeof(bf16) +
-         (size_t)(2 + 2 * LA_WARPS) * LA_ROWS * sizeof(float) + LA_ROWS * sizeof(int);
+size_t latent_smem(int dk, int rows) {
+  return (size_t)(rows + 2 * LA_BN) * (dk + LA_PAD) * sizeof(bf16) + (size_t)rows * LA_PS_LD * sizeof(bf16) +
+         (size_t)(2 + 2 * LA_WARPS) * rows * sizeof(float) + rows * sizeof(int);
 }
 
-template <int NG>
+template <int NG, int WG>
 int launch_latent(const LatentParams& p, dim3 grid, cudaStream_t stream) {
-  const size_t smem = latent_smem(p.dk);
+  const size_t smem = latent_smem(p.dk, LA_ROWS * WG);
   if (smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(latent_attention_kernel<NG>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(latent_attention_kernel<NG, WG>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return hfee_fail(HFEE_ERR_CUDA, "latent_attention_mma: %s", cudaGetErrorString(e));
   }
-  hfee_launch(latent_attention_kernel<NG>, grid, dim3(LA_THREADS), smem, stream, p);
+  hfee_launch(latent_attention_kernel<NG, WG>, grid, dim3(LA_THREADS * WG), smem, stream, p);
   return hfee_check_launch("latent_attention_mma");
 }
 
@@ -285,7 +289,7 @@ int launch_latent(const LatentParams& p, dim3 grid, cudaStream_t stream) {
 // 1 if the kernel takes these sizes: key size a multiple of 16 that fits shared memory, value size a multiple of 16
 // of at most 512 and at most the key size.
 HFEE_API int hfee_latent_attention_mma_supports(int heads, int dk, int dv) {
-  return heads > 0 && dk > 0 && dk % 16 == 0 && dv > 0 && dv % 16 == 0 && dv <= dk && dv <= 512 && latent_smem(dk) <= 227 * 1024;
+  return heads > 0 && dk > 0 && dk % 16 == 0 && dv > 0 && dv % 16 == 0 && dv <= dk && dv <= 512 && latent_smem(dk, LA_ROWS) <= 227 * 1024;
 }
 
 HFEE_API int hfee_latent_attention_mma(const void* q, long long ld_q, const void* pool, const int* block_table, int max_pages,
@@ -304,16 +308,25 @@ HFEE_API int hfee_latent_attention_mma(const void* q, long long ld_q, const void
   while ((1 << p.page_shift) < page_size) ++p.page_shift;
   p.cu_tokens = cu_tokens; p.slots = slots; p.context_before = context_before;
   p.heads = heads; p.dk = dk; p.dv = dv;
-  p.rows_per_token = heads < LA_ROWS ? heads : LA_ROWS;
-  p.tokens_per_tile = LA_ROWS / p.rows_per_token;
+  // two sets of warps where their rows can be filled (several tokens of a portion, or many heads) and fit shared memory
+  const int sets = ((long long)max_new * heads >= 2 * LA_ROWS && latent_smem(dk, 2 * LA_ROWS) <= 227 * 1024) ? 2 : 1;
+  const int rows = LA_ROWS * sets;
+  p.rows_per_token = heads < rows ? heads : rows;
+  p.tokens_per_tile = rows / p.rows_per_token;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.window = window;
   const dim3 grid((unsigned)((max_new + p.tokens_per_tile - 1) / p.tokens_per_tile),
                   (unsigned)((heads + p.rows_per_token - 1) / p.rows_per_token), (unsigned)requests);
   HFEE_REQUIRE(grid.y <= 65535, "latent_attention_mma: too many heads");
   const int per_warp = (dv / 16 + LA_WARPS - 1) / LA_WARPS;
-  if (per_warp <= 1) return launch_latent<1>(p, grid, stream);
-  if (per_warp <= 2) return launch_latent<2>(p, grid, stream);
-  if (per_warp <= 4) return launch_latent<4>(p, grid, stream);
-  return launch_latent<8>(p, grid, stream);
+  if (sets == 2) {
+    if (per_warp <= 1) return launch_latent<1, 2>(p, grid, stream);
+    if (per_warp <= 2) return launch_latent<2, 2>(p, grid, stream);
+    if (per_warp <= 4) return launch_latent<4, 2>(p, grid, stream);
+    return launch_latent<8, 2>(p, grid, stream);
+  }
+  if (per_warp <= 1) return launch_latent<1, 1>(p, grid, stream);
+  if (per_warp <= 2) return launch_latent<2, 1>(p, grid, stream);
+  if (per_warp <= 4) return launch_latent<4, 1>(p, grid, stream);
+  return launch_latent<8, 1>(p, grid, stream);
 }

@@ -41,7 +41,8 @@ __device__ __forceinline__ float rotated(const T* __restrict__ x, int d, int rop
   return v * cs[2 * i] + to_f32<T>(x[d - half]) * cs[2 * i + 1];
 }
 
-template <typename T>
+// PER_LANE: dimensions of a head per lane (heads of at most 32 * PER_LANE dimensions)
+template <typename T, int PER_LANE>
 __global__ void __launch_bounds__(RN_WARPS * 32)
 rope_norm_cache_kernel(const T* __restrict__ src, long long ld_src, int n, const float* __restrict__ cs, int rope_dim,
                        float norm_eps, const int* __restrict__ positions, const int* __restrict__ slot_of_token,
@@ -75,10 +76,10 @@ rope_norm_cache_kernel(const T* __restrict__ src, long long ld_src, int n, const
     csr = nullptr;
   }
   const T* x = row + g.src_off + (long long)h * g.src_stride;
-  float v[RN_PER_LANE];
+  float v[PER_LANE];
   float ss = 0.f;
 #pragma unroll
-  for (int j = 0; j < RN_PER_LANE; ++j) {
+  for (int j = 0; j < PER_LANE; ++j) {
     const int d = lane + 32 * j;
     v[j] = d < g.len ? rotated<T>(x, d, g.rope_off, rope_dim, csr) : 0.f;
     ss = fmaf(v[j], v[j], ss);
@@ -86,7 +87,7 @@ rope_norm_cache_kernel(const T* __restrict__ src, long long ld_src, int n, const
   float scale = 1.f;
   if (norm) scale = 1.0f / sqrtf(warp_sum(ss) / (float)g.len + norm_eps);
 #pragma unroll
-  for (int j = 0; j < RN_PER_LANE; ++j) {
+  for (int j = 0; j < PER_LANE; ++j) {
     const int d = lane + 32 * j;
     if (d < g.len) dst[d] = from_f32<T>(v[j] * scale);
   }
@@ -147,8 +148,19 @@ int launch_rope_norm(const void* src, long long ld_src, int n, const float* cs, 
   const long long tasks = (long long)n * (qg.count + kg.count + vg.count);
   if (tasks == 0) return HFEE_OK;
   const unsigned blocks = (unsigned)((tasks + RN_WARPS - 1) / RN_WARPS);
-  hfee_launch(rope_norm_cache_kernel<T>, dim3(blocks), dim3(RN_WARPS * 32), 0, stream, (const T*)src, ld_src, n, cs, rope_dim,
-              norm_eps, positions, slot_of_token, qg, (T*)q_out, ld_q, kg, (T*)k_pool, kc, vg, (T*)v_pool, vc);
+  int longest = 0;
+  if (qg.count) longest = qg.len;
+  if (kg.count && kg.len > longest) longest = kg.len;
+  if (vg.count && vg.len > longest) longest = vg.len;
+#define HFEE_RN(P)                                                                                                          \
+  hfee_launch(rope_norm_cache_kernel<T, P>, dim3(blocks), dim3(RN_WARPS * 32), 0, stream, (const T*)src, ld_src, n, cs, rope_dim, \
+              norm_eps, positions, slot_of_token, qg, (T*)q_out, ld_q, kg, (T*)k_pool, kc, vg, (T*)v_pool, vc)
+  if (longest <= 32) HFEE_RN(1);
+  else if (longest <= 64) HFEE_RN(2);
+  else if (longest <= 128) HFEE_RN(4);
+  else if (longest <= 256) HFEE_RN(8);
+  else HFEE_RN(RN_PER_LANE);
+#undef HFEE_RN
   return hfee_check_launch("rope_norm_cache");
 }
 

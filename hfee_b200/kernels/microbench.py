@@ -10,6 +10,11 @@ where that matters, and prints what it achieved against the roofline that bounds
     python -m hfee_b200.kernels.microbench attention_prefill --tokens 2048 --heads 32 --kv-heads 8 --head-dim 64
     python -m hfee_b200.kernels.microbench sigmoid_attention --tokens 2048 --heads 32 --kv-heads 8 --head-dim 64 --chunk 128
     python -m hfee_b200.kernels.microbench linear_attention  --tokens 2048 --heads 32 --head-dim 64 [--batch 8 for a decode step]
+    python -m hfee_b200.kernels.microbench delta_rule        --tokens 2048 --heads 32 --kv-heads 8 --head-dim 64 [--decode --batch 8]
+    python -m hfee_b200.kernels.microbench conv_act          --tokens 2048 --heads 32 --kv-heads 8 --head-dim 64
+    python -m hfee_b200.kernels.microbench latent_attention  --tokens 2048 --heads 32 --head-dim 64 --rank 256 --window 512 [--decode --batch 8]
+    python -m hfee_b200.kernels.microbench head_linear       --tokens 2048 --heads 32 --head-dim 64 --rank 256
+    python -m hfee_b200.kernels.microbench rope_norm_cache   --tokens 2048 --heads 32 --kv-heads 8 --head-dim 64
 
 ``--iters`` timed launches follow ``--warmup`` untimed ones; ``--rotate`` distinct weight
 buffers are cycled so that a weight-streaming kernel never finds its weights in L2.  The
@@ -189,9 +194,102 @@ def _linear_attention(args) -> dict:
             "us": round(sec * 1e6, 2), "tflops": round(flops / sec / 1e12, 2), "gbs": round(moved / sec / 1e9, 1)}
 
 
+def _delta_rule(args) -> dict:
+    """The gated delta rule: one prompt portion or a decode step of ``--batch`` requests (key and value size ``--head-dim``,
+    ``--kv-heads`` query/key heads)."""
+    heads, g, d = args.heads, args.kv_heads, args.head_dim
+    before, new = ([args.context] * args.batch, [1] * args.batch) if args.decode else ([0], [args.tokens])
+    b = _batch_of(before, new)
+    qkv = (torch.randn(b.n, 2 * g * d + heads * d, device=DEV) * 0.5).to(torch.bfloat16)
+    ba = torch.randn(b.n, 2 * heads, device=DEV).to(torch.bfloat16)
+    a_log, dt_bias = torch.linspace(-4.0, 1.0, heads, device=DEV), torch.linspace(-3.0, 1.0, heads, device=DEV)
+    state = torch.zeros(b.r, heads, d, d, device=DEV)
+    out = torch.empty(b.n, heads * d, dtype=torch.float32, device=DEV)
+    fn = lambda i: ops.delta_rule(qkv, 0, g * d, 2 * g * d, ba, 0, heads, a_log, dt_bias, state, b, out, heads, g, d, d)
+    sec = _time(fn, args.warmup, args.iters)
+    moved = b.n * (2 * g * d + heads * d) * 2 + b.n * heads * d * 4 + 2 * b.r * heads * d * d * 4
+    flops = b.n * heads * 6.0 * d * d
+    return {"kernel": "delta_rule", "heads": heads, "qk_heads": g, "dim": d, "requests": b.r, "tokens": b.n,
+            "us": round(sec * 1e6, 2), "tflops": round(flops / sec / 1e12, 3), "gbs": round(moved / sec / 1e9, 1)}
+
+
+def _conv_act(args) -> dict:
+    heads, g, d = args.heads, args.kv_heads, args.head_dim
+    b = _batch_of([0], [args.tokens])
+    width = 2 * g * d + heads * d
+    x = torch.randn(b.n, width + 8, device=DEV).to(torch.bfloat16)[:, :width]
+    w = torch.randn(width, 4, device=DEV)
+    state = torch.zeros(1, 3, width, device=DEV)
+    out = torch.empty(b.n, width, dtype=torch.bfloat16, device=DEV)
+    sec = _time(lambda i: ops.conv_act(x, w, state, b, out, "silu", True), args.warmup, args.iters)
+    return {"kernel": "conv_act", "width": width, "tokens": b.n, "us": round(sec * 1e6, 2),
+            "gbs": round(2 * b.n * width * 2 / sec / 1e9, 1)}
+
+
+def _latent_attention(args) -> dict:
+    """Attention over one cached vector per token of ``--rank`` + ``--head-dim``/2 dimensions whose first ``--rank`` are the values."""
+    heads, rank, page, window = args.heads, args.rank, args.page_size, args.window
+    dk = rank + args.head_dim // 2
+    before, new = ([args.context] * args.batch, [1] * args.batch) if args.decode else ([args.context_before], [args.tokens])
+    b = _batch_of(before, new)
+    max_pages = -(-b.max_context // page)
+    table = torch.randperm(b.r * max_pages).reshape(b.r, max_pages).to(torch.int32).to(DEV)
+    pool = torch.randn(b.r * max_pages, 1, page, dk, device=DEV).to(torch.bfloat16)
+    q = (torch.randn(b.n, heads * dk, device=DEV) * 0.3).to(torch.bfloat16)
+    out = torch.empty(b.n, heads * rank, dtype=torch.bfloat16, device=DEV)
+    ops.USE_LATENT_MMA = not args.no_tc_attention
+    fn = lambda i: ops.latent_attention(q, pool, table, page, b, out, heads, dk, rank, dk ** -0.5, window)
+    sec = _time(fn, args.warmup, args.iters)
+    keys = sum(min(p + 1, window) if window else p + 1 for s, c in zip(before, new) for p in range(s, s + c))
+    flops = 2.0 * heads * (dk + rank) * keys
+    moved = b.n * heads * (dk + rank) * 2 + sum(min(s + c, (window or s + c) + c) for s, c in zip(before, new)) * dk * 2
+    return {"kernel": "latent_attention", "heads": heads, "key_dim": dk, "value_dim": rank, "window": window, "requests": b.r,
+            "tokens": b.n, "us": round(sec * 1e6, 2), "tflops": round(flops / sec / 1e12, 2), "gbs": round(moved / sec / 1e9, 1)}
+
+
+def _head_linear(args) -> dict:
+    """The two per-head products of a latent attention: queries folded onto the latent (head_dim -> rank) and the attended
+    latent expanded to values (rank -> head_dim)."""
+    heads, d, rank, n = args.heads, args.head_dim, args.rank, args.tokens
+    r = d // 2
+    qh = torch.randn(n, heads * (d + r), device=DEV).to(torch.bfloat16)
+    w_fold = (torch.randn(heads, rank, d, device=DEV) * 0.1).to(torch.bfloat16)
+    qf = torch.empty(n, heads * (rank + r), dtype=torch.bfloat16, device=DEV)
+    ol = torch.randn(n, heads * rank, device=DEV).to(torch.bfloat16)
+    w_uv = (torch.randn(heads, d, rank, device=DEV) * 0.1).to(torch.bfloat16)
+    att = torch.empty(n, heads * d, dtype=torch.bfloat16, device=DEV)
+    gate = torch.randn(n, heads, device=DEV).to(torch.bfloat16)
+    fold = _time(lambda i: ops.head_linear(qh, 0, d + r, w_fold, qf, 0, rank + r), args.warmup, args.iters)
+    expand = _time(lambda i: ops.head_linear(ol, 0, rank, w_uv, att, 0, d, gate), args.warmup, args.iters)
+    flops = 2.0 * n * heads * d * rank
+    return {"kernel": "head_linear", "heads": heads, "head_dim": d, "rank": rank, "tokens": n,
+            "fold_us": round(fold * 1e6, 2), "fold_tflops": round(flops / fold / 1e12, 1),
+            "fold_gbs": round(n * heads * (d + rank) * 2 / fold / 1e9, 1),
+            "expand_us": round(expand * 1e6, 2), "expand_tflops": round(flops / expand / 1e12, 1),
+            "expand_gbs": round(n * heads * (d + rank) * 2 / expand / 1e9, 1)}
+
+
+def _rope_norm_cache(args) -> dict:
+    heads, kv, d, page = args.heads, args.kv_heads, args.head_dim, args.page_size
+    b = _batch_of([0], [args.tokens])
+    max_pages = -(-b.n // page)
+    table = torch.randperm(max_pages).reshape(1, max_pages).to(torch.int32).to(DEV)
+    kp = torch.empty(max_pages, kv, page, d, dtype=torch.bfloat16, device=DEV)
+    vp = torch.empty_like(kp)
+    cols = (heads + 2 * kv) * d
+    proj = torch.randn(b.n, cols, device=DEV).to(torch.bfloat16)
+    cs = torch.rand(b.n, d // 2, 2, device=DEV)
+    q = torch.empty(b.n, heads * d, dtype=torch.bfloat16, device=DEV)
+    fn = lambda i: ops.rope_norm_cache(proj, cs, d, 1e-5, b.positions, b.slot_of_token, table, page, q=(heads, 0, d, d, 0, q, 0, d),
+                                       k=(kv, heads * d, d, d, 0, kp, 0), v=((heads + kv) * d, d, d, vp))
+    sec = _time(fn, args.warmup, args.iters)
+    return {"kernel": "rope_norm_cache", "tokens": b.n, "us": round(sec * 1e6, 2), "gbs": round(2 * b.n * cols * 2 / sec / 1e9, 1)}
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("kernel", choices=["gemm_tcgen05", "gemm_stream", "gemm_skinny", "gemm_ring", "gemm_pair", "attention_decode", "attention_prefill",
+    ap.add_argument("kernel", choices=["delta_rule", "conv_act", "latent_attention", "head_linear", "rope_norm_cache",
+                                       "gemm_tcgen05", "gemm_stream", "gemm_skinny", "gemm_ring", "gemm_pair", "attention_decode", "attention_prefill",
                                       "sigmoid_attention", "linear_attention"])
     ap.add_argument("--m", type=int, default=2048)
     ap.add_argument("--n", type=int, default=16384)
@@ -208,6 +306,8 @@ def main(argv=None) -> int:
     ap.add_argument("--head-dim", type=int, default=64)
     ap.add_argument("--page-size", type=int, default=64)
     ap.add_argument("--splits", type=int, default=0)
+    ap.add_argument("--rank", type=int, default=256, help="latent_attention / head_linear: size of the key/value latent")
+    ap.add_argument("--window", type=int, default=512, help="latent_attention: sliding window (0: all earlier positions)")
     ap.add_argument("--chunk", type=int, default=128, help="sigmoid_attention: positions per block of the mask")
     ap.add_argument("--decode", action="store_true", help="sigmoid_attention / linear_attention: a decode step of --batch requests")
     ap.add_argument("--warmup", type=int, default=3)
@@ -226,6 +326,9 @@ def main(argv=None) -> int:
         res = _sigmoid_attention(args)
     elif args.kernel == "linear_attention":
         res = _linear_attention(args)
+    elif args.kernel in ("delta_rule", "conv_act", "latent_attention", "head_linear", "rope_norm_cache"):
+        res = {"delta_rule": _delta_rule, "conv_act": _conv_act, "latent_attention": _latent_attention,
+               "head_linear": _head_linear, "rope_norm_cache": _rope_norm_cache}[args.kernel](args)
     else:
         res = _attention(args, args.kernel == "attention_decode")
     print(json.dumps(res))

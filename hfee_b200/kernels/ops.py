@@ -364,7 +364,7 @@ def gemm_simt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: b
 
 STREAM_MAX_TOKENS = 64
 USE_TCGEN05 = True
-EPI_STORE, EPI_ACCUM, EPI_SWIGLU, EPI_GEGLU = 0, 1, 2, 4
+EPI_STORE, EPI_ACCUM, EPI_SWIGLU, EPI_GEGLU, EPI_RELU2 = 0, 1, 2, 4, 5      # 5 (tcgen05 kernels only): store relu(x)^2
 EPI_GATED = (EPI_SWIGLU, EPI_GEGLU)         # out = act(gate) * up over rows of w interleaved as [4 gate | 4 up]
 
 
@@ -1027,7 +1027,12 @@ def latent_mma_supports(heads: int, cached_dim: int, value_dim: int) -> bool:
 
 
 def linear_act(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, activation: str) -> None:
-    """out = act(a @ w.T) for an activation of :data:`UNARY_ACTIVATIONS`."""
+    """out = act(a @ w.T) for an activation of :data:`UNARY_ACTIVATIONS`: in the product's epilogue where the
+    large-tile tcgen05 kernels take the shape, else by a pass of its own over the result."""
+    if (activation == "relu2" and USE_TCGEN05 and not _streamable(a, w) and _tensor_core_ok(a, w)
+            and out.dtype == torch.bfloat16):
+        gemm_tcgen05(a, w, out, EPI_RELU2)
+        return
     linear(a, w, out)
     unary_act(out, out, activation)
 
