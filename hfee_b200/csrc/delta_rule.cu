@@ -367,6 +367,262 @@ delta_rule_kernel(const T* __restrict__ qkv, const T* __restrict__ ba, const flo
   }
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// The same in two kernels, for steps with portions of several tokens: everything that does not depend on the state is
+// computed for all tiles at once by `delta_prepare` (unit vectors, beta, the running log-decays and the tables: one
+// block per tile and head), and `delta_solve` walks a request's tiles with what is left: the products with S_0, the
+// substitution and the update of S.  A tile's place in the workspace is (first token of the tile) / 16 + request, which
+// differs for any two tiles of a step.
+constexpr int DW_HEAD = 2 * DR_TILE * DR_TILE + 3 * DR_TILE;       // tables, e^L, e^(L_last - L), beta
+
+__host__ __device__ inline int dw_dim(int dim) { return (dim + 3) / 4 * 4; }
+__host__ __device__ inline long long dw_qk_floats(int dim) { return 2ll * DR_TILE * dw_dim(dim); }
+
+template <typename T>
+__global__ void __launch_bounds__(128)
+delta_prepare_kernel(const T* __restrict__ qkv, const T* __restrict__ ba, const float* __restrict__ a_log,
+                     const float* __restrict__ dt_bias, const int* __restrict__ cu_tokens, float* __restrict__ ws_head,
+                     float* __restrict__ ws_qk, DeltaArgs p) {
+  extern __shared__ float smem[];
+  const int dim = p.dim, DP = dim + 1, DPW = dw_dim(dim);
+  float* q_s = smem;
+  float* k_s = q_s + DR_TILE * DP;
+  __shared__ float beta_s[DR_TILE], raw_s[DR_TILE], lg_s[DR_TILE];
+  const int req = blockIdx.z, h = blockIdx.y, tile0 = blockIdx.x * DR_TILE;
+  const int begin = cu_tokens[req], count = cu_tokens[req + 1] - begin;
+  pdl_wait();
+  pdl_launch_dependents();
+  if (tile0 >= count) return;
+  const int tt = min(DR_TILE, count - tile0);
+  const long long tok0 = begin + tile0;
+  const long long place = tok0 / DR_TILE + req;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int group = p.heads / p.qk_heads, kh = h / group;
+  for (int e = tid; e < DR_TILE * DP; e += 128) {
+    const int t = e / DP, d = e - t * DP;
+    const bool in = t < tt && d < dim;
+    const T* row = qkv + (tok0 + (in ? t : 0)) * p.ld_qkv + (long long)kh * dim + (in ? d : 0);
+    q_s[e] = in ? to_f32<T>(row[p.q_off]) : 0.f;
+    k_s[e] = in ? to_f32<T>(row[p.k_off]) : 0.f;
+  }
+  if (tid < DR_TILE) {
+    float b = 0.f, r = 0.f;
+    if (tid < tt) {
+      const T* row = ba + (tok0 + tid) * p.ld_ba;
+      b = 1.f / (1.f + expf(-to_f32<T>(row[p.b_off + h])));
+      r = -expf(a_log[h]) * softplus_f32(to_f32<T>(row[p.a_off + h]) + dt_bias[h]);
+    }
+    beta_s[tid] = b;
+    raw_s[tid] = r;
+  }
+  __syncthreads();
+  const float q_scale = 1.0f / sqrtf((float)dim);
+  for (int vid = warp; vid < 2 * tt; vid += 4) {
+    float* vec = vid < tt ? q_s + vid * DP : k_s + (vid - tt) * DP;
+    float ss = 0.f;
+    for (int d = lane; d < dim; d += 32) ss = fmaf(vec[d], vec[d], ss);
+    const float scale = (vid < tt ? q_scale : 1.f) / sqrtf(warp_sum(ss) + 1e-6f);
+    for (int d = lane; d < dim; d += 32) vec[d] *= scale;
+  }
+  float* wh = ws_head + (place * p.heads + h) * DW_HEAD;
+  if (tid < DR_TILE) {
+    float mine = 0.f, all = 0.f;
+    for (int t = 0; t < tt; ++t) {
+      all += raw_s[t];
+      if (t == tid) mine = all;
+    }
+    lg_s[tid] = mine;
+    wh[2 * DR_TILE * DR_TILE + tid] = tid < tt ? expf(mine) : 0.f;
+    wh[2 * DR_TILE * DR_TILE + DR_TILE + tid] = tid < tt ? expf(all - mine) : 0.f;
+    wh[2 * DR_TILE * DR_TILE + 2 * DR_TILE + tid] = beta_s[tid];
+  }
+  __syncthreads();
+  for (int e = tid; e < 2 * DR_TILE * DR_TILE; e += 128) {
+    const int row = e / DR_TILE, j = e - row * DR_TILE;
+    const int t = row & (DR_TILE - 1);
+    const bool second = row >= DR_TILE;
+    float c = 0.f;
+    if (t < tt && (second ? j <= t : j < t)) {
+      const float* kj = k_s + j * DP;
+      const float* xt = (second ? q_s : k_s) + t * DP;
+      float d0 = 0.f, d1 = 0.f;
+      int d = 0;
+      for (; d + 1 < dim; d += 2) {
+        d0 = fmaf(kj[d], xt[d], d0);
+        d1 = fmaf(kj[d + 1], xt[d + 1], d1);
+      }
+      if (d < dim) d0 = fmaf(kj[d], xt[d], d0);
+      const float dec = expf(lg_s[t] - lg_s[j]);
+      c = second ? dec * (d0 + d1) : -beta_s[t] * dec * (d0 + d1);
+    }
+    wh[e] = c;
+  }
+  if (h % group == 0) {
+    float* wq = ws_qk + (place * p.qk_heads + kh) * dw_qk_floats(dim);
+    for (int e = tid; e < DR_TILE * DPW; e += 128) {
+      const int t = e / DPW, d = e - t * DPW;
+      wq[e] = d < dim ? q_s[t * DP + d] : 0.f;
+      wq[DR_TILE * DPW + e] = d < dim ? k_s[t * DP + d] : 0.f;
+    }
+  }
+}
+
+template <typename T, int R>
+__global__ void __launch_bounds__(DR_THREADS)
+delta_solve_kernel(const T* __restrict__ qkv, const float* __restrict__ ws_head, const float* __restrict__ ws_qk,
+                   float* __restrict__ state, const int* __restrict__ cu_tokens, const int* __restrict__ slots,
+                   float* __restrict__ out, DeltaArgs p) {
+  extern __shared__ __align__(16) float smem[];
+  const int dim = p.dim, vdim = p.vdim, DPW = dw_dim(dim);
+  float* q_s = smem;                         // [DR_TILE][DPW]
+  float* k_s = q_s + DR_TILE * DPW;          // [DR_TILE][DPW]
+  __shared__ float v_s[DR_TILE][DR_COLS], o_s[DR_TILE][DR_COLS], el_s[DR_TILE], er_s[DR_TILE], beta_s[DR_TILE];
+  __shared__ float C_s[2 * DR_TILE][DR_TILE + 1];
+  constexpr int PER = (2 * DR_TILE * 32 * R / 4 + DR_THREADS - 1) / DR_THREADS;      // float4 pieces of q and k per thread
+  const int req = blockIdx.z, h = blockIdx.y, col0 = blockIdx.x * DR_COLS;
+  const int begin = cu_tokens[req], count = cu_tokens[req + 1] - begin;
+  const int slot = slots[req];
+  pdl_wait();
+  pdl_launch_dependents();
+  if (count <= 0) return;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int col = col0 + warp;
+  const int kh = h / (p.heads / p.qk_heads);
+  float* sp = state + (((long long)slot * p.heads + h) * dim) * vdim + col;
+  float S[R];
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+    const int i = lane + 32 * r;
+    S[r] = (i < dim && col < vdim) ? sp[(long long)i * vdim] : 0.f;
+  }
+  const int qk_pieces = 2 * DR_TILE * DPW / 4;
+  float4 pre_qk[PER], pre_head;
+  float pre_v;
+  auto fetch = [&](int first) {
+    const long long tok = begin + first, place = tok / DR_TILE + req;
+    const float4* src = reinterpret_cast<const float4*>(ws_qk + (place * p.qk_heads + kh) * dw_qk_floats(dim));
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+      const int pi = tid + i * DR_THREADS;
+      pre_qk[i] = pi < qk_pieces ? src[pi] : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    pre_head = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (tid < DW_HEAD / 4) pre_head = reinterpret_cast<const float4*>(ws_head + (place * p.heads + h) * DW_HEAD)[tid];
+    pre_v = 0.f;
+    if (tid < DR_TILE * DR_COLS) {
+      const int t = tid / DR_COLS, c = tid - t * DR_COLS;
+      if (first + t < count && col0 + c < vdim)
+        pre_v = to_f32<T>(qkv[(tok + t) * p.ld_qkv + p.v_off + (long long)h * vdim + col0 + c]);
+    }
+  };
+  fetch(0);
+  for (int tile0 = 0; tile0 < count; tile0 += DR_TILE) {
+    const int tt = min(DR_TILE, count - tile0);
+    const long long tok0 = begin + tile0;
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+      const int pi = tid + i * DR_THREADS;
+      if (pi < qk_pieces) reinterpret_cast<float4*>(q_s)[pi] = pre_qk[i];     // q rows, then k rows, as in the workspace
+    }
+    if (tid < DW_HEAD / 4) {
+      const float vals[4] = {pre_head.x, pre_head.y, pre_head.z, pre_head.w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int at = 4 * tid + e;
+        if (at < 2 * DR_TILE * DR_TILE) C_s[at / DR_TILE][at % DR_TILE] = vals[e];
+        else if (at < 2 * DR_TILE * DR_TILE + DR_TILE) el_s[at - 2 * DR_TILE * DR_TILE] = vals[e];
+        else if (at < 2 * DR_TILE * DR_TILE + 2 * DR_TILE) er_s[at - 2 * DR_TILE * DR_TILE - DR_TILE] = vals[e];
+        else beta_s[at - 2 * DR_TILE * DR_TILE - 2 * DR_TILE] = vals[e];
+      }
+    }
+    if (tid < DR_TILE * DR_COLS) v_s[tid / DR_COLS][tid % DR_COLS] = pre_v;
+    if (tile0 + DR_TILE < count) fetch(tile0 + DR_TILE);
+    __syncthreads();
+    float val[2 * DR_TILE];
+#pragma unroll
+    for (int t = 0; t < DR_TILE; ++t) {
+      float sk = 0.f, sq = 0.f;
+      const float* kt = k_s + t * DPW + lane;
+      const float* qt = q_s + t * DPW + lane;
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+        if (lane + 32 * r < DPW) {
+          sk = fmaf(S[r], kt[32 * r], sk);
+          sq = fmaf(S[r], qt[32 * r], sq);
+        }
+      }
+      val[t] = sk;
+      val[DR_TILE + t] = sq;
+    }
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) {
+      const bool upper = (lane & off) != 0;
+#pragma unroll
+      for (int i = 0; i < off; ++i) {
+        const float send = upper ? val[i] : val[i + off];
+        const float keep = upper ? val[i + off] : val[i];
+        val[i] = keep + __shfl_xor_sync(0xffffffffu, send, off);
+      }
+    }
+    const int t_mine = lane & (DR_TILE - 1);
+    float x = 0.f;
+    if (t_mine < tt) x = lane < DR_TILE ? beta_s[t_mine] * (v_s[t_mine][warp] - el_s[t_mine] * val[0]) : el_s[t_mine] * val[0];
+    const float carry = el_s[tt - 1];
+#pragma unroll
+    for (int r = 0; r < R; ++r) S[r] *= carry;
+#pragma unroll
+    for (int j = 0; j < DR_TILE; ++j) {
+      if (j < tt) {
+        const float uj = __shfl_sync(0xffffffffu, x, j);
+        x = fmaf(C_s[lane][j], uj, x);
+        const float w = uj * er_s[j];
+        const float* kj = k_s + j * DPW + lane;
+#pragma unroll
+        for (int r = 0; r < R; ++r)
+          if (lane + 32 * r < DPW) S[r] = fmaf(kj[32 * r], w, S[r]);
+      }
+    }
+    if (lane >= DR_TILE && t_mine < tt) o_s[t_mine][warp] = x;
+    __syncthreads();
+    if (tid < tt * DR_COLS) {
+      const int t = tid / DR_COLS, c = tid - t * DR_COLS;
+      if (col0 + c < vdim) out[(tok0 + t) * p.ld_out + (long long)h * vdim + col0 + c] = o_s[t][c];
+    }
+  }
+  if (p.write_state) {
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      const int i = lane + 32 * r;
+      if (i < dim && col < vdim) sp[(long long)i * vdim] = S[r];
+    }
+  }
+}
+
+template <typename T, int R>
+int launch_solve_r(const void* qkv, const float* ws_head, const float* ws_qk, float* state, const int* cu_tokens,
+                   const int* slots, float* out, const DeltaArgs& p, int requests, cudaStream_t stream) {
+  const size_t smem = (size_t)2 * DR_TILE * dw_dim(p.dim) * sizeof(float);
+  hfee_launch(delta_solve_kernel<T, R>, dim3((unsigned)((p.vdim + DR_COLS - 1) / DR_COLS), (unsigned)p.heads, (unsigned)requests),
+              dim3(DR_THREADS), smem, stream, (const T*)qkv, ws_head, ws_qk, state, cu_tokens, slots, out, p);
+  return hfee_check_launch("delta_solve");
+}
+
+template <typename T>
+int launch_prepared(const void* qkv, const void* ba, const float* a_log, const float* dt_bias, float* state,
+                    const int* cu_tokens, const int* slots, float* out, const DeltaArgs& p, int requests, int max_new,
+                    float* ws_head, float* ws_qk, cudaStream_t stream) {
+  const size_t smem = (size_t)2 * DR_TILE * (p.dim + 1) * sizeof(float);
+  hfee_launch(delta_prepare_kernel<T>, dim3((unsigned)((max_new + DR_TILE - 1) / DR_TILE), (unsigned)p.heads, (unsigned)requests),
+              dim3(128), smem, stream, (const T*)qkv, (const T*)ba, a_log, dt_bias, cu_tokens, ws_head, ws_qk, p);
+  int rc = hfee_check_launch("delta_prepare");
+  if (rc != HFEE_OK) return rc;
+  const int r = (p.dim + 31) / 32;
+  if (r <= 1) return launch_solve_r<T, 1>(qkv, ws_head, ws_qk, state, cu_tokens, slots, out, p, requests, stream);
+  if (r <= 2) return launch_solve_r<T, 2>(qkv, ws_head, ws_qk, state, cu_tokens, slots, out, p, requests, stream);
+  if (r <= 4) return launch_solve_r<T, 4>(qkv, ws_head, ws_qk, state, cu_tokens, slots, out, p, requests, stream);
+  return launch_solve_r<T, 8>(qkv, ws_head, ws_qk, state, cu_tokens, slots, out, p, requests, stream);
+}
+
 template <typename T, int R>
 int launch_delta_r(const void* qkv, const void* ba, const float* a_log, const float* dt_bias, float* state,
                    const int* cu_tokens, const int* slots, float* out, const DeltaArgs& p, int requests, cudaStream_t stream) {
@@ -409,14 +665,22 @@ HFEE_API int hfee_conv_act(const void* x, long long ld_x, int dtype, const float
   return hfee_fail(HFEE_ERR_ARG, "conv_act: unknown dtype %d", dtype);
 }
 
+// Floats of workspace the two-kernel form needs for a step of n_tokens tokens in `requests` requests.
+HFEE_API long long hfee_delta_rule_workspace(int requests, int n_tokens, int heads, int qk_heads, int dim) {
+  const long long places = n_tokens / DR_TILE + requests + 1;
+  return places * ((long long)heads * DW_HEAD + (long long)qk_heads * dw_qk_floats(dim));
+}
+
+// With a workspace (see hfee_delta_rule_workspace) and a portion of more than one token in the step (max_new > 1), the
+// step runs as two kernels (delta_prepare, delta_solve); else as one.
 // qkv rows: head g's query at q_off + g * dim, its key at k_off + g * dim (g < qk_heads; head h of `heads` uses
 // g = h / (heads / qk_heads)), head h's value at v_off + h * vdim.  ba rows: b_off + h and a_off + h.
 // state: [slots, heads, dim, vdim] float32.  out: float32 [n, heads * vdim].
 HFEE_API int hfee_delta_rule(const void* qkv, long long ld_qkv, int q_off, int k_off, int v_off, const void* ba,
                              long long ld_ba, int b_off, int a_off, int dtype, const float* a_log, const float* dt_bias,
                              float* state, const int* cu_tokens, const int* slots, float* out, long long ld_out,
-                             int requests, int heads, int qk_heads, int dim, int vdim, int write_state,
-                             cudaStream_t stream) {
+                             int requests, int heads, int qk_heads, int dim, int vdim, int write_state, int n_tokens,
+                             int max_new, float* workspace, long long workspace_floats, cudaStream_t stream) {
   if (requests == 0) return HFEE_OK;
   HFEE_REQUIRE(heads > 0 && qk_heads > 0 && heads % qk_heads == 0, "delta_rule: heads %d must be a multiple of %d", heads, qk_heads);
   HFEE_REQUIRE(dim > 0 && dim <= DR_MAX_DIM && vdim > 0, "delta_rule: key size %d is outside 1..%d", dim, DR_MAX_DIM);
@@ -424,6 +688,19 @@ HFEE_API int hfee_delta_rule(const void* qkv, long long ld_qkv, int q_off, int k
   const int vec = dim % vec_elems == 0 && ld_qkv % vec_elems == 0 && q_off % vec_elems == 0 && k_off % vec_elems == 0 &&
                   (uintptr_t)qkv % 16 == 0;
   DeltaArgs p{ld_qkv, ld_ba, ld_out, q_off, k_off, v_off, b_off, a_off, heads, qk_heads, dim, vdim, write_state, vec};
+  if (workspace != nullptr && max_new > 1) {
+    // portions of several tokens: the state-independent part of every tile first, in parallel
+    HFEE_REQUIRE(workspace_floats >= hfee_delta_rule_workspace(requests, n_tokens, heads, qk_heads, dim) && (uintptr_t)workspace % 16 == 0,
+                 "delta_rule: the workspace is too small or not 16-byte aligned");
+    const long long places = n_tokens / DR_TILE + requests + 1;
+    float* ws_head = workspace;
+    float* ws_qk = workspace + places * heads * DW_HEAD;
+    if (dtype == HFEE_F32)
+      return launch_prepared<float>(qkv, ba, a_log, dt_bias, state, cu_tokens, slots, out, p, requests, max_new, ws_head, ws_qk, stream);
+    if (dtype == HFEE_BF16)
+      return launch_prepared<__nv_bfloat16>(qkv, ba, a_log, dt_bias, state, cu_tokens, slots, out, p, requests, max_new, ws_head, ws_qk, stream);
+    return hfee_fail(HFEE_ERR_ARG, "delta_rule: unknown dtype %d", dtype);
+  }
   if (dtype == HFEE_F32)
     return launch_delta<float>(qkv, ba, a_log, dt_bias, state, cu_tokens, slots, out, p, requests, stream);
   if (dtype == HFEE_BF16)

@@ -205,7 +205,8 @@ def _delta_rule(args) -> dict:
     a_log, dt_bias = torch.linspace(-4.0, 1.0, heads, device=DEV), torch.linspace(-3.0, 1.0, heads, device=DEV)
     state = torch.zeros(b.r, heads, d, d, device=DEV)
     out = torch.empty(b.n, heads * d, dtype=torch.float32, device=DEV)
-    fn = lambda i: ops.delta_rule(qkv, 0, g * d, 2 * g * d, ba, 0, heads, a_log, dt_bias, state, b, out, heads, g, d, d)
+    ws = torch.empty(ops.delta_rule_workspace(b.r, b.n, heads, g, d), dtype=torch.float32, device=DEV)
+    fn = lambda i: ops.delta_rule(qkv, 0, g * d, 2 * g * d, ba, 0, heads, a_log, dt_bias, state, b, out, heads, g, d, d, True, ws)
     sec = _time(fn, args.warmup, args.iters)
     moved = b.n * (2 * g * d + heads * d) * 2 + b.n * heads * d * 4 + 2 * b.r * heads * d * d * 4
     flops = b.n * heads * 6.0 * d * d

@@ -70,7 +70,7 @@ _SIGNATURES = {
     "hfee_head_linear": [_P, _L, _I, _I, _P, _P, _L, _I, _I, _I, _I, _I, _I, _P, _L, _I, _P],
     "hfee_conv_act": [_P, _L, _I, _P, _P, _P, _P, _P, _L, _I, _I, _I, _I, _I, _I, _P],
     "hfee_conv_act_launches": [_I, _I, _I],
-    "hfee_delta_rule": [_P, _L, _I, _I, _I, _P, _L, _I, _I, _I, _P, _P, _P, _P, _P, _P, _L, _I, _I, _I, _I, _I, _I, _P],
+    "hfee_delta_rule": [_P, _L, _I, _I, _I, _P, _L, _I, _I, _I, _P, _P, _P, _P, _P, _P, _L, _I, _I, _I, _I, _I, _I, _I, _I, _P, _L, _P],
     "hfee_head_norm_gate": [_P, _L, _P, _F, _P, _L, _P, _L, _I, _I, _I, _I, _I, _P],
     "hfee_unary_act": [_P, _L, _P, _L, _I, _I, _I, _I, _P],
     "hfee_head_gate": [_P, _L, _P, _L, _I, _I, _I, _I, _P],
@@ -101,6 +101,8 @@ def library() -> ctypes.CDLL:
     lib.hfee_attention_tc_supports.restype = _I
     lib.hfee_linear_attention_chunked_workspace.restype = _L
     lib.hfee_linear_attention_chunked_workspace.argtypes = [_I, _I, _I, _I, _I]
+    lib.hfee_delta_rule_workspace.restype = _L
+    lib.hfee_delta_rule_workspace.argtypes = [_I, _I, _I, _I, _I]
     for name, sig in _SIGNATURES.items():
         try:
             fn = getattr(lib, name)
@@ -1121,12 +1123,14 @@ def conv_act(x: torch.Tensor, weight: torch.Tensor, state: torch.Tensor, step, o
 
 def delta_rule(qkv: torch.Tensor, q_off: int, k_off: int, v_off: int, ba: torch.Tensor, b_off: int, a_off: int,
                a_log: torch.Tensor, dt_bias: torch.Tensor, state: torch.Tensor, step, out: torch.Tensor, heads: int,
-               qk_heads: int, dim: int, vdim: int, write_state: bool = True) -> None:
+               qk_heads: int, dim: int, vdim: int, write_state: bool = True, workspace: Optional[torch.Tensor] = None) -> None:
     """The gated delta rule over the step's tokens, continuing each request's float32 state ``state``
     [slots, heads, dim, vdim]: S <- g S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q, with q and k made unit
     vectors per head first (q also times dim^-1/2), beta = sigmoid(b) and g = exp(-exp(a_log) softplus(a + dt_bias)).
     ``qkv`` rows hold the queries and keys of ``qk_heads`` heads and the values of ``heads`` heads at the given
-    column offsets, ``ba`` rows one b and one a per head.  ``out`` is float32 [n, heads * vdim]."""
+    column offsets, ``ba`` rows one b and one a per head.  ``out`` is float32 [n, heads * vdim].  With ``workspace``
+    (float32, see :func:`delta_rule_workspace`) a step that has a portion of several tokens runs as two kernels: what
+    does not depend on the state for all tiles of 16 tokens at once, then the walk over each request's tiles."""
     lib = library()
     n = qkv.shape[0]
     assert qkv.dtype == ba.dtype and ba.shape[0] == n and out.dtype == torch.float32 and tuple(out.shape) == (n, heads * vdim)
@@ -1134,10 +1138,19 @@ def delta_rule(qkv: torch.Tensor, q_off: int, k_off: int, v_off: int, ba: torch.
     assert state.dtype == torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == (heads, dim, vdim)
     assert max(q_off, k_off) + qk_heads * dim <= qkv.shape[1] and v_off + heads * vdim <= qkv.shape[1]
     assert max(b_off, a_off) + heads <= ba.shape[1]
+    assert workspace is None or (workspace.dtype == torch.float32 and workspace.is_contiguous())
     _check(lib.hfee_delta_rule(qkv.data_ptr(), _rows(qkv, "qkv"), q_off, k_off, v_off, ba.data_ptr(), _rows(ba, "ba"), b_off,
                                a_off, _dt(qkv), a_log.data_ptr(), dt_bias.data_ptr(), state.data_ptr(),
                                step.cu_tokens.data_ptr(), step.slots.data_ptr(), out.data_ptr(), _rows(out, "out"), step.r,
-                               heads, qk_heads, dim, vdim, int(write_state), _stream()), lib)
+                               heads, qk_heads, dim, vdim, int(write_state), step.n, step.max_new, _ptr(workspace),
+                               workspace.numel() if workspace is not None else 0, _stream()), lib)
+    if workspace is not None and step.max_new > 1:
+        count_launches(1)
+
+
+def delta_rule_workspace(requests: int, tokens: int, heads: int, qk_heads: int, dim: int) -> int:
+    """Floats of workspace the two-kernel delta rule needs for a step of ``tokens`` tokens in ``requests`` requests."""
+    return int(library().hfee_delta_rule_workspace(requests, tokens, heads, qk_heads, dim))
 
 
 def head_norm_gate(x: torch.Tensor, weight: torch.Tensor, eps: float, gate: torch.Tensor, out: torch.Tensor, heads: int,

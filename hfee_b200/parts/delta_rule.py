@@ -81,9 +81,14 @@ class GatedDeltaRule(Mixer):
         ops.conv_act(proj[:, :self.conv_cols], self.conv_weight, cache.states["conv"], step, qkv, "silu", writes_cache)
         o = rt.scratch("delta_out", (rt.max_tokens, self.vg_cols), torch.float32)[:n]
         ops.tag("delta_rule")
+        workspace = None
+        if step.max_new > 1:
+            # the state-independent part of every tile of 16 tokens; sized once for the engine's limits
+            workspace = rt.scratch("delta_tiles", (ops.delta_rule_workspace(
+                rt.max_requests, rt.max_tokens, self.heads, self.qk_heads, self.key_dim),), torch.float32)
         ops.delta_rule(qkv, 0, self.qk_cols, 2 * self.qk_cols, proj, self.b_at, self.a_at, self.a_log, self.dt_bias,
                        cache.states["recurrent"], step, o, self.heads, self.qk_heads, self.key_dim, self.value_dim,
-                       writes_cache)
+                       writes_cache, workspace)
         gated = rt.scratch("delta_gated", (rt.max_tokens, pad8(self.vg_cols)))[:n, :self.vg_cols]
         ops.tag("gate")
         ops.head_norm_gate(o, self.norm_weight, self.eps, proj[:, self.g_at:self.g_at + self.vg_cols], gated, self.heads,
