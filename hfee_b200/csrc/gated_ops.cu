@@ -295,6 +295,59 @@ void launch_rmsnorm_add(const float* y, long long ld_y, const float* w, float* r
 }
 }  // namespace
 
+namespace {
+// residual += y / sqrt(mean(y^2) + eps) * w, then out = residual / sqrt(mean(residual^2) + eps2) * w2: the norm on a
+// sublayer's output and the norm in front of the next sublayer in one pass over the row (kept in shared memory).
+template <typename T>
+__global__ void __launch_bounds__(ROW_THREADS)
+rmsnorm_add_norm_kernel(const float* __restrict__ y, long long ld_y, const float* __restrict__ w, float* __restrict__ residual,
+                        int width, float eps, int add_unit, const float* __restrict__ w2, float eps2, int add_unit2,
+                        T* __restrict__ out, long long ld_o) {
+  extern __shared__ float row_s[];
+  __shared__ float partial[ROW_THREADS / 32];
+  pdl_wait();
+  pdl_launch_dependents();
+  const float* yr = y + (long long)blockIdx.x * ld_y;
+  float* rr = residual + (long long)blockIdx.x * width;
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < width; c += ROW_THREADS) {
+    const float v = yr[c];
+    row_s[c] = v;
+    ss = fmaf(v, v, ss);
+  }
+  const float scale = 1.0f / sqrtf(block_sum(ss, partial) / (float)width + eps);
+  float ss2 = 0.f;
+  for (int c = threadIdx.x; c < width; c += ROW_THREADS) {
+    const float r = rr[c] + row_s[c] * scale * (add_unit ? 1.f + w[c] : w[c]);
+    rr[c] = r;
+    row_s[c] = r;
+    ss2 = fmaf(r, r, ss2);
+  }
+  const float scale2 = 1.0f / sqrtf(block_sum(ss2, partial) / (float)width + eps2);
+  T* orow = out + (long long)blockIdx.x * ld_o;
+  for (int c = threadIdx.x; c < width; c += ROW_THREADS)
+    orow[c] = from_f32<T>(row_s[c] * scale2 * (add_unit2 ? 1.f + w2[c] : w2[c]));
+}
+}  // namespace
+
+HFEE_API int hfee_rmsnorm_add_norm(const float* y, long long ld_y, const float* w, float* residual, int n, int width,
+                                   float eps, int add_unit, const float* w2, float eps2, int add_unit2, void* out,
+                                   long long ld_o, int out_dtype, cudaStream_t stream) {
+  if (n == 0) return HFEE_OK;
+  HFEE_REQUIRE(n > 0 && width > 0 && ld_y >= width && ld_o >= width, "rmsnorm_add_norm: bad sizes");
+  HFEE_REQUIRE((size_t)width * sizeof(float) <= 48 * 1024, "rmsnorm_add_norm: width %d does not fit shared memory", width);
+  const size_t smem = (size_t)width * sizeof(float);
+  if (out_dtype == HFEE_BF16)
+    hfee_launch(rmsnorm_add_norm_kernel<__nv_bfloat16>, dim3(n), dim3(ROW_THREADS), smem, stream, y, ld_y, w, residual, width, eps,
+                add_unit, w2, eps2, add_unit2, (__nv_bfloat16*)out, ld_o);
+  else if (out_dtype == HFEE_F32)
+    hfee_launch(rmsnorm_add_norm_kernel<float>, dim3(n), dim3(ROW_THREADS), smem, stream, y, ld_y, w, residual, width, eps, add_unit,
+                w2, eps2, add_unit2, (float*)out, ld_o);
+  else
+    return hfee_fail(HFEE_ERR_ARG, "rmsnorm_add_norm: unknown dtype %d", out_dtype);
+  return hfee_check_launch("rmsnorm_add_norm");
+}
+
 // residual += norm(y); with cast_out the new residual row is also written there in the activations' type
 HFEE_API int hfee_rmsnorm_add(const float* y, long long ld_y, const float* w, float* residual, int n, int width,
                               float eps, int add_unit, void* cast_out, long long ld_c, int cast_dtype, cudaStream_t stream) {

@@ -56,6 +56,7 @@ _SIGNATURES = {
     "hfee_linear_attention": [_P, _P, _P, _L, _I, _P, _P, _P, _P, _P, _L, _I, _I, _I, _I, _I, _I, _P],
     "hfee_linear_attention_chunked": [_P, _P, _P, _L, _I, _P, _P, _P, _P, _P, _L, _P, _L, _I, _I, _I, _I, _I, _I, _I, _I, _P],
     "hfee_rmsnorm_add": [_P, _L, _P, _P, _I, _I, _F, _I, _P, _L, _I, _P],
+    "hfee_rmsnorm_add_norm": [_P, _L, _P, _P, _I, _I, _F, _I, _P, _F, _I, _P, _L, _I, _P],
     "hfee_norm_gate": [_P, _L, _P, _F, _P, _L, _P, _L, _I, _I, _I, _P],
     "hfee_gated_act": [_P, _L, _P, _L, _I, _I, _I, _I, _I, _P],
     "hfee_scale_f32": [_P, _L, _I, _I, _F, _P],
@@ -1198,6 +1199,22 @@ def rmsnorm_add(y: torch.Tensor, weight: torch.Tensor, residual: torch.Tensor, e
                                 _dt(cast_out) if cast_out is not None else 0, _stream()), lib)
 
 
+RMSNORM_ADD_NORM_MAX_WIDTH = 12288          # the row is kept in shared memory
+
+
+def rmsnorm_add_norm(y: torch.Tensor, weight: torch.Tensor, residual: torch.Tensor, eps: float, weight2: torch.Tensor,
+                     eps2: float, out: torch.Tensor, add_unit: bool = False, add_unit2: bool = False) -> None:
+    """residual += y * rsqrt(mean(y^2) + eps) * weight, then out = residual * rsqrt(mean(residual^2) + eps2) * weight2
+    in ``out``'s dtype: the norm on a sublayer's output and the norm in front of the next sublayer in one kernel."""
+    lib = library()
+    assert y.dtype == residual.dtype == weight.dtype == weight2.dtype == torch.float32 and residual.is_contiguous()
+    n, width = residual.shape
+    assert y.shape == residual.shape == out.shape and weight.numel() == weight2.numel() == width
+    _check(lib.hfee_rmsnorm_add_norm(y.data_ptr(), _rows(y, "y"), weight.data_ptr(), residual.data_ptr(), n, width, float(eps),
+                                     int(add_unit), weight2.data_ptr(), float(eps2), int(add_unit2), out.data_ptr(),
+                                     _rows(out, "out"), _dt(out), _stream()), lib)
+
+
 def norm_gate(x: torch.Tensor, weight: Optional[torch.Tensor], eps: float, gate: torch.Tensor, out: torch.Tensor) -> None:
     """out = (x * rsqrt(mean(x^2) + eps) * weight) * sigmoid(gate); without ``weight`` only the gate.
     ``x`` is float32; ``gate`` and ``out`` share a dtype."""
@@ -1340,7 +1357,7 @@ def argmax(logits: torch.Tensor, out: torch.Tensor, scratch: torch.Tensor, slots
 
 
 # the entry points the parts and the sampler launch through can be left out by class (see tag())
-for _name in ("latent_attention", "linear_act", "attention_simt_general", "rope_norm_cache", "latent_norm_rope_cache", "head_linear", "conv_act", "delta_rule",
+for _name in ("rmsnorm_add_norm", "latent_attention", "linear_act", "attention_simt_general", "rope_norm_cache", "latent_norm_rope_cache", "head_linear", "conv_act", "delta_rule",
               "head_norm_gate", "unary_act", "head_gate", "attention_simt_masked", "short_conv", "linear_attention", "rmsnorm_add", "norm_gate", "gated_act", "scale_", "cast_rows", "sigmoid_attention",
               "qk_norm_rope_cache", "embed", "rmsnorm", "rope_table", "rope_cache_write", "swiglu", "linear", "linear_normed", "linear_swiglu", "linear_rope_cache",
               "linear_swiglu_normed", "paged_attention", "paged_attention_rope", "sample", "argmax", "sample_chain"):

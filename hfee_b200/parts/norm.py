@@ -40,9 +40,13 @@ class RMSNorm(Part):
         the new residual in the dtype the next matrix product reads.  With ``then`` (another norm) the new
         residual, normed by it, goes to ``then_out``: the input of the sublayer that follows."""
         before = ops.tag("norm")
-        ops.rmsnorm_add(y, self.weight, residual, self.eps, add_unit=self.add_unit, cast_out=cast_out)
-        if then is not None:
-            ops.rmsnorm(residual, then.weight, then_out, then.eps, add_unit=then.add_unit)
+        if then is not None and cast_out is None and residual.shape[1] <= ops.RMSNORM_ADD_NORM_MAX_WIDTH:
+            ops.rmsnorm_add_norm(y, self.weight, residual, self.eps, then.weight, then.eps, then_out,
+                                 add_unit=self.add_unit, add_unit2=then.add_unit)
+        else:
+            ops.rmsnorm_add(y, self.weight, residual, self.eps, add_unit=self.add_unit, cast_out=cast_out)
+            if then is not None:
+                ops.rmsnorm(residual, then.weight, then_out, then.eps, add_unit=then.add_unit)
         ops.tag(before)
 
     def fused_params(self):

@@ -35,12 +35,12 @@ def models(tmp_path_factory):
     return out
 
 
-def check(got, ref, dtype, what=""):
+def check(got, ref, dtype, what="", rms_tol=None):
     assert sorted(got) == list(range(len(ref)))
     for i in range(len(ref)):
         assert got[i].shape == ref[i].shape
         err, rms = ru.rel_err(got[i], ref[i]), rms_err(got[i], ref[i])
-        assert err < TOL[dtype] and rms < RMS_TOL[dtype], f"{what} request {i}: relative error {err:.3g}, rms {rms:.3g}"
+        assert err < TOL[dtype] and rms < (rms_tol or RMS_TOL[dtype]), f"{what} request {i}: relative error {err:.3g}, rms {rms:.3g}"
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -95,6 +95,24 @@ def test_each_mixer_alone(tmp_path, layer, dtype):
     ref = [plain.forward(c, w, s) for s in seqs]
     for steps in (ru.whole(seqs), ru.portions(seqs, sizes=(2, 9, 1, 1, 30, 2))):
         check(ru.run_in_process(bu.make_runner(d, dtype, 64, max_requests=1), steps), ref, dtype)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_sizes_that_fit_no_vector_access(tmp_path, dtype):
+    """Width, vocabulary, ranks and head sizes that are multiples of neither 8 nor 4: every kernel takes its scalar path."""
+    layers = [bu.delta(3, 1, 12, 10, 3, ff=36),
+              bu.latent(3, 10, 6, 14, 18, 22, window=5, base=77.0, scale=0.4, ff=30),
+              bu.attention(2, 1, 12, 10, 6, 300.0, 0.35, scaling=(3.0, 1.0, 5.0, 20))]
+    cfg = bu.config(50, 77, layers + [bu.again(layers, 0)], eps=3e-6)
+    d = bu.write_model(str(tmp_path), cfg, seed=13)
+    c, w = plain.load(d)
+    seqs = bu.sequences(77, (41, 2, 19), seed=6)
+    ref = [plain.forward(c, w, s) for s in seqs]
+    # bfloat16: sums over ten to fifty terms average less of the rounding than the wider models' sums do (measured 1.8e-2;
+    # the float32 run of the same kernels' float32 instances holds the usual bound)
+    rms_tol = 2.5e-2 if dtype == "bfloat16" else None
+    for steps in (ru.whole(seqs), ru.portions(seqs, sizes=(3, 2, 17, 1, 5)), ru.mixed(seqs, live=2, seed=1)):
+        check(ru.run_in_process(bu.make_runner(d, dtype, 96, max_requests=2, context=48), steps), ref, dtype, rms_tol=rms_tol)
 
 
 @pytest.mark.parametrize("taps", [1, 2, 5])
