@@ -23,13 +23,31 @@ constexpr int CA_THREADS = 128;
 constexpr int CA_OUT = 1, CA_STATE = 2;
 constexpr int ACT_NONE = 0, ACT_SILU = 1;
 
-template <typename T>
+// CH = channels per thread: 2 (one 4- or 8-byte access for both) for even widths and row strides, else 1.
+template <typename T, int CH> struct ChanIO;
+template <typename T> struct ChanIO<T, 1> {
+  static __device__ __forceinline__ void load(const T* p, float (&v)[1]) { v[0] = to_f32<T>(*p); }
+  static __device__ __forceinline__ void store(T* p, const float (&v)[1]) { *p = from_f32<T>(v[0]); }
+};
+template <> struct ChanIO<float, 2> {
+  static __device__ __forceinline__ void load(const float* p, float (&v)[2]) { const float2 t = *reinterpret_cast<const float2*>(p); v[0] = t.x; v[1] = t.y; }
+  static __device__ __forceinline__ void store(float* p, const float (&v)[2]) { *reinterpret_cast<float2*>(p) = make_float2(v[0], v[1]); }
+};
+template <> struct ChanIO<__nv_bfloat16, 2> {
+  static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&v)[2]) {
+    const __nv_bfloat162 t = *reinterpret_cast<const __nv_bfloat162*>(p);
+    v[0] = __bfloat162float(t.x); v[1] = __bfloat162float(t.y);
+  }
+  static __device__ __forceinline__ void store(__nv_bfloat16* p, const float (&v)[2]) { *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(v[0], v[1]); }
+};
+
+template <typename T, int CH>
 __global__ void __launch_bounds__(CA_THREADS)
 conv_act_kernel(const T* __restrict__ x, long long ld_x, const float* __restrict__ w, float* __restrict__ state,
                 const int* __restrict__ cu_tokens, const int* __restrict__ slots, T* __restrict__ out, long long ld_out,
                 int width, int taps, int act, int mode) {
   const int req = blockIdx.y;
-  const int c = blockIdx.z * CA_THREADS + threadIdx.x;
+  const int c = (blockIdx.z * CA_THREADS + threadIdx.x) * CH;
   const int begin = cu_tokens[req], count = cu_tokens[req + 1] - begin;     // host-written batch layout
   const int slot = slots[req];
   pdl_wait();
@@ -41,29 +59,48 @@ conv_act_kernel(const T* __restrict__ x, long long ld_x, const float* __restrict
   const int last = min(count, first + CA_TOKENS);
   float* st = state + (long long)slot * hist * width + c;                    // st[s * width]: input at index s - hist
   const T* xc = x + (long long)begin * ld_x + c;
-  float wv[CA_MAX_TAPS], win[CA_MAX_TAPS];
+  float wv[CH][CA_MAX_TAPS], win[CA_MAX_TAPS][CH];
 #pragma unroll
   for (int j = 0; j < CA_MAX_TAPS; ++j) {
-    wv[j] = j < taps ? w[(long long)c * taps + j] : 0.f;
-    win[j] = 0.f;
+#pragma unroll
+    for (int k = 0; k < CH; ++k) {
+      wv[k][j] = j < taps ? w[(long long)(c + k) * taps + j] : 0.f;
+      win[j][k] = 0.f;
+    }
     if (j < hist) {
       const int s = first - hist + j;
-      win[j] = s >= 0 ? to_f32<T>(xc[(long long)s * ld_x]) : st[(long long)(hist + s) * width];
+      if (s >= 0) ChanIO<T, CH>::load(xc + (long long)s * ld_x, win[j]);
+      else ChanIO<float, CH>::load(st + (long long)(hist + s) * width, win[j]);
     }
   }
   if (mode & CA_OUT) {
-    for (int t = first; t < last; ++t) {
-      const float xv = to_f32<T>(xc[(long long)t * ld_x]);
-      float acc = 0.f;
+    float xin[CA_TOKENS][CH];                 // the run's inputs, requested together
 #pragma unroll
-      for (int j = 0; j < CA_MAX_TAPS; ++j) {
-        const float in = (j == hist) ? xv : win[j];
-        if (j < taps) acc = fmaf(wv[j], in, acc);
+    for (int i = 0; i < CA_TOKENS; ++i) {
+#pragma unroll
+      for (int k = 0; k < CH; ++k) xin[i][k] = 0.f;
+      if (first + i < last) ChanIO<T, CH>::load(xc + (long long)(first + i) * ld_x, xin[i]);
+    }
+#pragma unroll
+    for (int i = 0; i < CA_TOKENS; ++i) {
+      const int t = first + i;
+      if (t >= last) break;
+      float o[CH];
+#pragma unroll
+      for (int k = 0; k < CH; ++k) {
+        float acc = 0.f;
+#pragma unroll
+        for (int j = 0; j < CA_MAX_TAPS; ++j) {
+          const float in = (j == hist) ? xin[i][k] : win[j][k];
+          if (j < taps) acc = fmaf(wv[k][j], in, acc);
+        }
+        o[k] = act == ACT_SILU ? acc / (1.f + expf(-acc)) : acc;
       }
-      if (act == ACT_SILU) acc = acc / (1.f + expf(-acc));
-      out[(long long)(begin + t) * ld_out + c] = from_f32<T>(acc);
+      ChanIO<T, CH>::store(out + (long long)(begin + t) * ld_out + c, o);
 #pragma unroll
-      for (int j = 0; j + 1 < CA_MAX_TAPS; ++j) win[j] = (j + 1 == hist) ? xv : win[j + 1];
+      for (int j = 0; j + 1 < CA_MAX_TAPS; ++j)
+#pragma unroll
+        for (int k = 0; k < CH; ++k) win[j][k] = (j + 1 == hist) ? xin[i][k] : win[j + 1][k];
     }
   }
   if ((mode & CA_STATE) && last == count) {
@@ -71,24 +108,38 @@ conv_act_kernel(const T* __restrict__ x, long long ld_x, const float* __restrict
     // place than the one being written, so ascending order reads before it overwrites
     for (int s = 0; s < hist; ++s) {
       const int idx = count - hist + s;
-      st[(long long)s * width] = idx >= 0 ? to_f32<T>(xc[(long long)idx * ld_x]) : st[(long long)(hist + idx) * width];
+      float v[CH];
+      if (idx >= 0) ChanIO<T, CH>::load(xc + (long long)idx * ld_x, v);
+      else ChanIO<float, CH>::load(st + (long long)(hist + idx) * width, v);
+      ChanIO<float, CH>::store(st + (long long)s * width, v);
     }
   }
+}
+
+template <typename T, int CH>
+int launch_conv_act_ch(const void* x, long long ld_x, const float* w, float* state, const int* cu_tokens, const int* slots,
+                       void* out, long long ld_out, int requests, int max_new, int width, int taps, int act, int write_state,
+                       cudaStream_t stream) {
+  const unsigned runs = (unsigned)((max_new + CA_TOKENS - 1) / CA_TOKENS);
+  const unsigned cz = (unsigned)((width / CH + CA_THREADS - 1) / CA_THREADS);
+  const bool together = write_state && runs == 1 && taps > 1;
+  hfee_launch(conv_act_kernel<T, CH>, dim3(runs, requests, cz), dim3(CA_THREADS), 0, stream, (const T*)x, ld_x, w, state, cu_tokens,
+              slots, (T*)out, ld_out, width, taps, act, together ? (CA_OUT | CA_STATE) : CA_OUT);
+  if (write_state && !together && taps > 1)
+    hfee_launch(conv_act_kernel<T, CH>, dim3(1, requests, cz), dim3(CA_THREADS), 0, stream, (const T*)x, ld_x, w, state, cu_tokens,
+                slots, (T*)out, ld_out, width, taps, act, CA_STATE);
+  return hfee_check_launch("conv_act");
 }
 
 template <typename T>
 int launch_conv_act(const void* x, long long ld_x, const float* w, float* state, const int* cu_tokens, const int* slots,
                     void* out, long long ld_out, int requests, int max_new, int width, int taps, int act, int write_state,
                     cudaStream_t stream) {
-  const unsigned runs = (unsigned)((max_new + CA_TOKENS - 1) / CA_TOKENS);
-  const unsigned cz = (unsigned)((width + CA_THREADS - 1) / CA_THREADS);
-  const bool together = write_state && runs == 1 && taps > 1;
-  hfee_launch(conv_act_kernel<T>, dim3(runs, requests, cz), dim3(CA_THREADS), 0, stream, (const T*)x, ld_x, w, state, cu_tokens,
-              slots, (T*)out, ld_out, width, taps, act, together ? (CA_OUT | CA_STATE) : CA_OUT);
-  if (write_state && !together && taps > 1)
-    hfee_launch(conv_act_kernel<T>, dim3(1, requests, cz), dim3(CA_THREADS), 0, stream, (const T*)x, ld_x, w, state, cu_tokens,
-                slots, (T*)out, ld_out, width, taps, act, CA_STATE);
-  return hfee_check_launch("conv_act");
+  const bool pairs = width % 2 == 0 && ld_x % 2 == 0 && ld_out % 2 == 0 && (uintptr_t)x % (2 * sizeof(T)) == 0 &&
+                     (uintptr_t)out % (2 * sizeof(T)) == 0 && (uintptr_t)state % 8 == 0;
+  if (pairs)
+    return launch_conv_act_ch<T, 2>(x, ld_x, w, state, cu_tokens, slots, out, ld_out, requests, max_new, width, taps, act, write_state, stream);
+  return launch_conv_act_ch<T, 1>(x, ld_x, w, state, cu_tokens, slots, out, ld_out, requests, max_new, width, taps, act, write_state, stream);
 }
 
 // ---------------------------------------------------------------------------------------------------------------

@@ -154,7 +154,7 @@ def run_in_process(runner, steps):
 
 def run_trace_binary(model_dir, dtype, steps, out_dir, max_tokens, vocab, extra_args=(), env=None):
     """Feed a trace to bin/trace_run over its standard input, waiting for ``done``
-    after each step as the contract requires; returns {rid: rows}."""
+    after each step, as its interface says; returns {rid: rows}."""
     cmd = [sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", model_dir, "--dtype", dtype,
            "--out", out_dir, "--max-tokens", str(max_tokens), *extra_args]
     p = subprocess.Popen(cmd, stdin=subprocess.PIPE, stdout=subprocess.PIPE, text=True, env=env)
