@@ -159,6 +159,27 @@ def test_window_and_page_edges(tmp_path, dtype, kind):
         assert ru.rel_err(got[0], ref) < TOL[dtype], f"cut {sizes[:5]}"
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("window", [1, 2, 16, 32, 33])
+def test_smallest_and_page_sized_windows(tmp_path, dtype, window):
+    """A window of one position (a token sees only itself), of two, of exactly one and two pages, and of one more:
+    pages behind the window go back to the pool while the request runs, in prompts and in decoding."""
+    layers = [bu.latent(2, 16, 16, 16, 16, 16, window=window, base=30.0, scale=0.5),
+              bu.attention(2, 1, 16, 16, 16, 30.0, 0.3, window=window)]
+    cfg = bu.config(32, 60, layers)
+    d = bu.write_model(str(tmp_path), cfg, seed=23)
+    c, w = plain.load(d)
+    seqs = bu.sequences(60, (70, 35), seed=4)
+    ref = [plain.forward(c, w, s) for s in seqs]
+    # the pool is smaller than what the two requests would hold without windows: 5 pages of 16 for 105 tokens
+    pool = 80 if window <= 16 else 112
+    for steps in (ru.portions(seqs, sizes=(15, 2, 17, 1, 1, 16, 2)), ru.prefill_then_decode(seqs, tail=30)):
+        runner = bu.make_runner(d, dtype, pool, page_size=16, max_requests=1, context=80)
+        if window <= 16:        # only the windowed groups exist, so the request never holds more than window / 16 + 2 pages
+            assert all(g.need.window == window for g in runner.cache.paged)
+        check(ru.run_in_process(runner, steps), ref, dtype, f"window={window}")
+
+
 def _far_sequences(first):
     """Two sequences of 400 tokens that differ in their first ``first`` tokens only (tokens 0 and 1 stand nowhere else)."""
     later = [2 + t % 48 for t in bu.sequences(50, (400 - first,), seed=8)[0]]
