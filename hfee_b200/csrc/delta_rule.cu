@@ -41,7 +41,13 @@ template <> struct ChanIO<__nv_bfloat16, 2> {
   static __device__ __forceinline__ void store(__nv_bfloat16* p, const float (&v)[2]) { *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(v[0], v[1]); }
 };
 
-template <typename T, int CH>
+// values that are rounded to bfloat16 on the way out take the fast exponential and division
+template <typename T> __device__ __forceinline__ float silu_out(float z);
+template <> __device__ __forceinline__ float silu_out<float>(float z) { return z / (1.f + expf(-z)); }
+template <> __device__ __forceinline__ float silu_out<__nv_bfloat16>(float z) { return __fdividef(z, 1.f + __expf(-z)); }
+
+// MAXT: the most taps this instance takes (4 or CA_MAX_TAPS): the window and the weights live in registers
+template <typename T, int CH, int MAXT>
 __global__ void __launch_bounds__(CA_THREADS)
 conv_act_kernel(const T* __restrict__ x, long long ld_x, const float* __restrict__ w, float* __restrict__ state,
                 const int* __restrict__ cu_tokens, const int* __restrict__ slots, T* __restrict__ out, long long ld_out,
@@ -59,9 +65,9 @@ conv_act_kernel(const T* __restrict__ x, long long ld_x, const float* __restrict
   const int last = min(count, first + CA_TOKENS);
   float* st = state + (long long)slot * hist * width + c;                    // st[s * width]: input at index s - hist
   const T* xc = x + (long long)begin * ld_x + c;
-  float wv[CH][CA_MAX_TAPS], win[CA_MAX_TAPS][CH];
+  float wv[CH][MAXT], win[MAXT][CH];
 #pragma unroll
-  for (int j = 0; j < CA_MAX_TAPS; ++j) {
+  for (int j = 0; j < MAXT; ++j) {
 #pragma unroll
     for (int k = 0; k < CH; ++k) {
       wv[k][j] = j < taps ? w[(long long)(c + k) * taps + j] : 0.f;
@@ -90,15 +96,15 @@ conv_act_kernel(const T* __restrict__ x, long long ld_x, const float* __restrict
       for (int k = 0; k < CH; ++k) {
         float acc = 0.f;
 #pragma unroll
-        for (int j = 0; j < CA_MAX_TAPS; ++j) {
+        for (int j = 0; j < MAXT; ++j) {
           const float in = (j == hist) ? xin[i][k] : win[j][k];
           if (j < taps) acc = fmaf(wv[k][j], in, acc);
         }
-        o[k] = act == ACT_SILU ? acc / (1.f + expf(-acc)) : acc;
+        o[k] = act == ACT_SILU ? silu_out<T>(acc) : acc;
       }
       ChanIO<T, CH>::store(out + (long long)(begin + t) * ld_out + c, o);
 #pragma unroll
-      for (int j = 0; j + 1 < CA_MAX_TAPS; ++j)
+      for (int j = 0; j + 1 < MAXT; ++j)
 #pragma unroll
         for (int k = 0; k < CH; ++k) win[j][k] = (j + 1 == hist) ? xin[i][k] : win[j + 1][k];
     }
@@ -123,10 +129,11 @@ int launch_conv_act_ch(const void* x, long long ld_x, const float* w, float* sta
   const unsigned runs = (unsigned)((max_new + CA_TOKENS - 1) / CA_TOKENS);
   const unsigned cz = (unsigned)((width / CH + CA_THREADS - 1) / CA_THREADS);
   const bool together = write_state && runs == 1 && taps > 1;
-  hfee_launch(conv_act_kernel<T, CH>, dim3(runs, requests, cz), dim3(CA_THREADS), 0, stream, (const T*)x, ld_x, w, state, cu_tokens,
+  auto kernel = taps <= 4 ? conv_act_kernel<T, CH, 4> : conv_act_kernel<T, CH, CA_MAX_TAPS>;
+  hfee_launch(kernel, dim3(runs, requests, cz), dim3(CA_THREADS), 0, stream, (const T*)x, ld_x, w, state, cu_tokens,
               slots, (T*)out, ld_out, width, taps, act, together ? (CA_OUT | CA_STATE) : CA_OUT);
   if (write_state && !together && taps > 1)
-    hfee_launch(conv_act_kernel<T, CH>, dim3(1, requests, cz), dim3(CA_THREADS), 0, stream, (const T*)x, ld_x, w, state, cu_tokens,
+    hfee_launch(kernel, dim3(1, requests, cz), dim3(CA_THREADS), 0, stream, (const T*)x, ld_x, w, state, cu_tokens,
                 slots, (T*)out, ld_out, width, taps, act, CA_STATE);
   return hfee_check_launch("conv_act");
 }
