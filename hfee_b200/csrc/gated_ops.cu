@@ -471,9 +471,9 @@ head_norm_gate_kernel(const float* __restrict__ x, long long ld_x, const float* 
   pdl_wait();
   pdl_launch_dependents();
   const int lane = threadIdx.x & 31;
-  const long long task = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
-  if (task >= (long long)n * heads) return;
-  const int i = (int)(task / heads), h = (int)(task % heads);
+  const unsigned task = blockIdx.x * 4 + (threadIdx.x >> 5);   // the launcher keeps n * heads below 2^31
+  if (task >= (unsigned)n * (unsigned)heads) return;
+  const int i = (int)(task / (unsigned)heads), h = (int)(task - (unsigned)i * (unsigned)heads);
   const float* xr = x + (long long)i * ld_x + (long long)h * head_dim;
   const T* gr = gate + (long long)i * ld_g + (long long)h * head_dim;
   T* orow = out + (long long)i * ld_o + (long long)h * head_dim;
@@ -524,6 +524,7 @@ HFEE_API int hfee_head_norm_gate(const float* x, long long ld_x, const float* w,
   const long long width = (long long)heads * head_dim;
   HFEE_REQUIRE(n > 0 && heads > 0 && head_dim > 0 && ld_x >= width && ld_g >= width && ld_o >= width, "head_norm_gate: bad sizes");
   HFEE_REQUIRE(act == HG_SIGMOID || act == HG_SILU, "head_norm_gate: unknown gate activation %d", act);
+  HFEE_REQUIRE((long long)n * heads < (1ll << 31), "head_norm_gate: too many (token, head) pairs for one launch");
   const unsigned blocks = (unsigned)(((long long)n * heads + 3) / 4);
   if (dtype == HFEE_F32)
     hfee_launch(head_norm_gate_kernel<float>, dim3(blocks), dim3(128), 0, stream, x, ld_x, w, eps, (const float*)gate, ld_g, (float*)out, ld_o, n, heads, head_dim, act);

@@ -52,10 +52,10 @@ rope_norm_cache_kernel(const T* __restrict__ src, long long ld_src, int n, const
   pdl_launch_dependents();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int per_token = qg.count + kg.count + vg.count;
-  const long long task = (long long)blockIdx.x * RN_WARPS + warp;
-  if (task >= (long long)n * per_token) return;
-  const int i = (int)(task / per_token);
-  int h = (int)(task % per_token);
+  const unsigned task = blockIdx.x * RN_WARPS + warp;          // the launcher keeps n * per_token below 2^31
+  if (task >= (unsigned)n * (unsigned)per_token) return;
+  const int i = (int)(task / (unsigned)per_token);
+  int h = (int)(task - (unsigned)i * (unsigned)per_token);
   const T* row = src + (long long)i * ld_src;
   const float* csr = cs != nullptr ? cs + (long long)i * rope_dim : nullptr;
   HeadGroup g;
@@ -147,6 +147,7 @@ int launch_rope_norm(const void* src, long long ld_src, int n, const float* cs, 
                      const PagedCache& vc, cudaStream_t stream) {
   const long long tasks = (long long)n * (qg.count + kg.count + vg.count);
   if (tasks == 0) return HFEE_OK;
+  if (tasks >= (1ll << 31)) return hfee_fail(HFEE_ERR_ARG, "rope_norm_cache: %lld (token, head) pairs exceed one launch", tasks);
   const unsigned blocks = (unsigned)((tasks + RN_WARPS - 1) / RN_WARPS);
   int longest = 0;
   if (qg.count) longest = qg.len;
